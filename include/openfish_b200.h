@@ -1,0 +1,73 @@
+/*
+ * openfish_b200.h -- entry points this library adds next to the openfish C API.
+ *
+ * Nothing here exists in the reference; a program written against the reference never needs
+ * this header.  It offers (a) error reporting that does not terminate the process, (b) decode
+ * calls that write into caller-owned host buffers instead of malloc'ing new ones on every
+ * call, split into submit and wait so that the caller can overlap the decode of one batch with
+ * other work (the reference's synchronous malloc + pageable copy, src/decode_cuda.cu:118-123
+ * and :206-211, costs as much as the kernels themselves at B200 speeds), and (c) the device
+ * times of the last decode for benchmarking.
+ */
+#ifndef OPENFISH_B200_H
+#define OPENFISH_B200_H
+
+#include "openfish/openfish.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status of the calling thread's most recent library call. */
+enum openfish_b200_status {
+    OPENFISH_B200_OK = 0,
+    OPENFISH_B200_ERR_ARGUMENT = 1,    /* NULL pointer, unsupported state_len, T or N < 1, ... */
+    OPENFISH_B200_ERR_LAYOUT = 2,      /* C < 4*4^state_len, C % 8 != 0, misaligned pointer */
+    OPENFISH_B200_ERR_SHAPE = 3,       /* T, N or state_len differ from the gpubuf's */
+    OPENFISH_B200_ERR_OPTION = 4,      /* beam_width != 32 */
+    OPENFISH_B200_ERR_ALLOC = 5,       /* host or device allocation failed */
+    OPENFISH_B200_ERR_CUDA = 6,        /* a CUDA call failed; see openfish_b200_error_text */
+    OPENFISH_B200_ERR_DEVICE_WAIT = 7, /* a kernel gave up waiting for an asynchronous copy */
+    OPENFISH_B200_ERR_NO_CPU_PATH = 8, /* openfish_decode_cpu / openfish_rotary_emb_cpu called */
+    OPENFISH_B200_ERR_TOO_LONG = 9     /* T beyond what one block's shared memory can trace back */
+};
+
+/* 0 (default): behave like the reference -- print the error and exit(EXIT_FAILURE).
+ * 1: print the error (subject to the log level), record it, and return to the caller; output
+ *    pointers are set to NULL and openfish_gpubuf_init returns NULL.  Process-wide. */
+void openfish_b200_set_error_mode(int keep_running);
+int openfish_b200_get_error_mode(void);
+
+/* Status of the calling thread's last call into the library, and a description of it. */
+int openfish_b200_last_status(void);
+const char *openfish_b200_error_text(void);
+
+/* Same work as openfish_decode_gpu, but the results land in buffers the caller owns: three host
+ * buffers of N*T bytes each (page-locked memory avoids a staging copy; pageable memory works
+ * too).  Nothing is malloc'ed. */
+void openfish_b200_decode_into(int T, int N, int C, const void *scores_TNC, int state_len,
+                               const openfish_opt_t *options, const openfish_gpubuf_t *gpubuf,
+                               uint8_t *moves, char *sequence, char *qstring);
+
+/* The same split in two: submit enqueues the kernels and the device-to-host copies on the
+ * gpubuf's stream and returns at once; wait blocks until they are done and reports the status.
+ * One decode may be in flight per gpubuf.  The three host buffers must be page-locked for the
+ * copies to be asynchronous. */
+void openfish_b200_decode_submit(int T, int N, int C, const void *scores_TNC, int state_len,
+                                 const openfish_opt_t *options, const openfish_gpubuf_t *gpubuf,
+                                 uint8_t *moves, char *sequence, char *qstring);
+void openfish_b200_decode_wait(const openfish_gpubuf_t *gpubuf);
+
+/* Device time, in milliseconds, of the gpubuf's last completed decode, measured with CUDA
+ * events on the stream the kernels ran on: ms[0] backward scan kernel, ms[1] fused forward /
+ * beam-search / sequence kernel, ms[2] device-to-host copies, ms[3] all of it. */
+void openfish_b200_last_decode_ms(const openfish_gpubuf_t *gpubuf, float ms[4]);
+
+/* Number of kernels one decode call launches (for benchmark bookkeeping). */
+int openfish_b200_kernels_per_decode(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* OPENFISH_B200_H */

@@ -1,0 +1,210 @@
+"""openfish_b200 -- Python mirror of the openfish C API, backed by ``lib/libopenfish.so``.
+
+The functions carry the reference's names and argument meaning (include/openfish/openfish.h):
+``gpubuf_init`` / ``gpubuf_free`` / ``decode_gpu`` / ``rotary_emb_gpu``.  Everything goes
+through the C ABI with plain device pointers; torch is used only to own device memory.  There
+is no CPU fallback: if the shared library is missing or cannot be loaded the import of this
+module's native half raises.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libopenfish.so")
+
+STATUS_NAMES = ["OK", "ERR_ARGUMENT", "ERR_LAYOUT", "ERR_SHAPE", "ERR_OPTION", "ERR_ALLOC",
+                "ERR_CUDA", "ERR_DEVICE_WAIT", "ERR_NO_CPU_PATH", "ERR_TOO_LONG"]
+
+
+class OpenfishError(RuntimeError):
+    def __init__(self, status, text):
+        super().__init__("%s: %s" % (STATUS_NAMES[status] if 0 <= status < len(STATUS_NAMES) else status, text))
+        self.status = status
+
+
+class Opt(C.Structure):
+    """openfish_opt_t (include/openfish/openfish.h)."""
+    _fields_ = [("beam_width", C.c_size_t), ("beam_cut", C.c_float), ("blank_score", C.c_float),
+                ("q_shift", C.c_float), ("q_scale", C.c_float), ("temperature", C.c_float),
+                ("move_pad", C.c_bool)]
+
+
+class GpuBufStruct(C.Structure):
+    """openfish_gpubuf_t (include/openfish/openfish.h): ten device pointers."""
+    _fields_ = [(n, C.c_void_p) for n in ("bwd_NTC", "post_NTC", "moves", "sequence", "qstring",
+                                          "beam_vector", "states", "qual_data", "base_probs",
+                                          "total_probs")]
+
+
+def decoder_init(**overrides):
+    """DECODER_INIT with optional field overrides."""
+    o = Opt(32, 100.0, 2.0, 0.0, 1.0, 1.0, False)
+    for k, v in overrides.items():
+        setattr(o, k, v)
+    return o
+
+
+# q_scale / q_shift the reference's driver applies per model (src/main.c:256-265)
+MODEL_QSCORE = {3: dict(q_scale=0.97, q_shift=-1.8), 4: dict(q_scale=0.95, q_shift=-0.2),
+                5: dict(q_scale=0.95, q_shift=0.5)}
+
+_lib = None
+
+
+def lib():
+    """The loaded shared library (raises if it is absent: there is no other implementation)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError("%s not found: build it with `python -m openfish_b200.build` "
+                              "(needs nvcc); openfish_b200 has no fallback path" % LIB_PATH)
+        L = C.CDLL(LIB_PATH)
+        vp, i = C.c_void_p, C.c_int
+        L.openfish_gpubuf_init.restype = C.POINTER(GpuBufStruct)
+        L.openfish_gpubuf_init.argtypes = [i, i, i]
+        L.openfish_gpubuf_free.restype = None
+        L.openfish_gpubuf_free.argtypes = [C.POINTER(GpuBufStruct)]
+        dec = [i, i, i, vp, i, C.POINTER(Opt), C.POINTER(GpuBufStruct)]
+        L.openfish_decode_gpu.restype = None
+        L.openfish_decode_gpu.argtypes = dec + [C.POINTER(vp)] * 3
+        for name in ("openfish_b200_decode_into", "openfish_b200_decode_submit"):
+            getattr(L, name).restype = None
+            getattr(L, name).argtypes = dec + [vp] * 3
+        L.openfish_b200_decode_wait.restype = None
+        L.openfish_b200_decode_wait.argtypes = [C.POINTER(GpuBufStruct)]
+        L.openfish_rotary_emb_gpu.restype = None
+        L.openfish_rotary_emb_gpu.argtypes = [vp, vp, vp] + [i] * 8
+        L.openfish_decode_cpu.restype = None
+        L.openfish_decode_cpu.argtypes = [i, i, i, i, vp, i, C.POINTER(Opt)] + [C.POINTER(vp)] * 3
+        L.openfish_b200_last_decode_ms.restype = None
+        L.openfish_b200_last_decode_ms.argtypes = [C.POINTER(GpuBufStruct), C.POINTER(C.c_float)]
+        L.openfish_b200_last_status.restype = i
+        L.openfish_b200_error_text.restype = C.c_char_p
+        L.openfish_b200_set_error_mode.argtypes = [i]
+        L.openfish_b200_kernels_per_decode.restype = i
+        L.get_openfish_log_level.restype = i
+        L.set_openfish_log_level.argtypes = [i]
+        # Python callers get exceptions instead of the reference's exit(1)
+        L.openfish_b200_set_error_mode(1)
+        L.libc_free = C.CDLL(None).free
+        L.libc_free.argtypes = [vp]
+        _lib = L
+    return _lib
+
+
+def _check():
+    st = lib().openfish_b200_last_status()
+    if st != 0:
+        raise OpenfishError(st, lib().openfish_b200_error_text().decode())
+
+
+class _DevView:
+    """Zero-copy window on device memory for torch.as_tensor (CUDA array interface)."""
+
+    def __init__(self, ptr, shape, typestr):
+        self.__cuda_array_interface__ = {"data": (ptr, False), "shape": tuple(shape),
+                                         "typestr": typestr, "version": 2}
+
+
+class GpuBuf:
+    """Device buffers for decodes of one shape; mirrors openfish_gpubuf_t's fields as torch
+    tensors (views, not copies)."""
+
+    def __init__(self, T, N, state_len):
+        self.T, self.N, self.state_len = T, N, state_len
+        self.ptr = lib().openfish_gpubuf_init(T, N, state_len)
+        _check()
+
+    def free(self):
+        if self.ptr:
+            lib().openfish_gpubuf_free(self.ptr)
+            self.ptr = None
+            _check()
+
+    def tensor(self, name):
+        import torch
+        T, N, ns = self.T, self.N, 4 ** self.state_len
+        spec = {"bwd_NTC": ((N, T + 1, ns), "<f4"), "post_NTC": ((N, T + 1, ns), "<f4"),
+                "moves": ((N, T), "|u1"), "sequence": ((N, T), "|u1"), "qstring": ((N, T), "|u1"),
+                "beam_vector": ((N, T + 1, 32), "|u1"), "states": ((N, T), "<i4"),
+                "qual_data": ((N, T, 4), "<f4"), "base_probs": ((N, T), "<f4"),
+                "total_probs": ((N, T), "<f4")}[name]
+        return torch.as_tensor(_DevView(getattr(self.ptr.contents, name), *spec), device="cuda")
+
+    def last_decode_ms(self):
+        ms = (C.c_float * 4)()
+        lib().openfish_b200_last_decode_ms(self.ptr, ms)
+        return dict(bwd_scan=ms[0], fwd_beam=ms[1], d2h=ms[2], total=ms[3])
+
+
+def gpubuf_init(T, N, state_len):
+    return GpuBuf(T, N, state_len)
+
+
+def gpubuf_free(gpubuf):
+    gpubuf.free()
+
+
+def _scores_args(scores_TNC, state_len, options, gpubuf):
+    import torch
+    if not (isinstance(scores_TNC, torch.Tensor) and scores_TNC.is_cuda
+            and scores_TNC.dtype == torch.float16 and scores_TNC.is_contiguous()
+            and scores_TNC.dim() == 3):
+        raise TypeError("scores_TNC must be a contiguous CUDA float16 tensor [T][N][C]")
+    T, N, Cc = scores_TNC.shape
+    return (T, N, Cc, scores_TNC.data_ptr(), state_len, C.byref(options or decoder_init()), gpubuf.ptr)
+
+
+def decode_gpu(scores_TNC, state_len, options=None, gpubuf=None):
+    """openfish_decode_gpu: returns dict(moves, sequence, qstring) of uint8 arrays [N][T]
+    (copies of the library's malloc'ed results, which are freed here)."""
+    own = gpubuf is None
+    if own:
+        gpubuf = GpuBuf(scores_TNC.shape[0], scores_TNC.shape[1], state_len)
+    try:
+        args = _scores_args(scores_TNC, state_len, options, gpubuf)
+        out = [C.c_void_p() for _ in range(3)]
+        lib().openfish_decode_gpu(*args, *[C.byref(o) for o in out])
+        _check()
+        T, N = args[0], args[1]
+        res = {}
+        for k, p in zip(("moves", "sequence", "qstring"), out):
+            res[k] = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint8)), shape=(N, T)).copy()
+            lib().libc_free(p)
+        return res
+    finally:
+        if own:
+            gpubuf.free()
+
+
+def decode_into(scores_TNC, state_len, gpubuf, moves, sequence, qstring, options=None, wait=True):
+    """openfish_b200_decode_into / _submit: results into caller-owned uint8 host tensors
+    [N][T] (torch, ideally pinned).  With wait=False call decode_wait(gpubuf) afterwards."""
+    args = _scores_args(scores_TNC, state_len, options, gpubuf)
+    fn = lib().openfish_b200_decode_into if wait else lib().openfish_b200_decode_submit
+    fn(*args, moves.data_ptr(), sequence.data_ptr(), qstring.data_ptr())
+    _check()
+
+
+def decode_wait(gpubuf):
+    lib().openfish_b200_decode_wait(gpubuf.ptr)
+    _check()
+
+
+def rotary_emb_gpu(x_gpu, sin_gpu, cos_gpu, batch_size, seqlen, nheads, head_dim, rotary_half,
+                   stride_batch, stride_seq, stride_head):
+    """openfish_rotary_emb_gpu on torch CUDA tensors (x float16 in place, sin/cos float32)."""
+    lib().openfish_rotary_emb_gpu(x_gpu.data_ptr(), sin_gpu.data_ptr(), cos_gpu.data_ptr(),
+                                  batch_size, seqlen, nheads, head_dim, rotary_half, stride_batch,
+                                  stride_seq, stride_head)
+    _check()
+
+
+def shard_range(n_chunks, rank, world):
+    """Contiguous chunk range [lo, hi) of `rank` when `n_chunks` chunks are split over `world`
+    GPUs by chunk index (earlier ranks take the remainder)."""
+    each, extra = divmod(n_chunks, world)
+    lo = rank * each + min(rank, extra)
+    return lo, lo + each + (1 if rank < extra else 0)

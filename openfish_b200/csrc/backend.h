@@ -1,0 +1,39 @@
+/* backend.h -- the thin C ABI between the C host layer (openfish_api.c) and the CUDA side
+ * (decode_b200.cu).  Plain C types only.  Every function returns an openfish_b200_status
+ * value and, on failure, leaves a description retrievable with ofb_error_text(). */
+#ifndef OFB_BACKEND_H
+#define OFB_BACKEND_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "openfish/openfish.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int ofb_gpubuf_create(int T, int N, int state_len, openfish_gpubuf_t **out);
+int ofb_gpubuf_destroy(openfish_gpubuf_t *gpubuf);
+/* Checks that gpubuf came from ofb_gpubuf_create with this shape. */
+int ofb_gpubuf_check(const openfish_gpubuf_t *gpubuf, int T, int N, int state_len);
+
+/* Enqueue one decode and the copies of moves/sequence/qstring into the three host buffers. */
+int ofb_decode_submit(int T, int N, int C, const void *scores, int state_len, float beam_cut,
+                      float blank_score, float q_shift, float q_scale,
+                      const openfish_gpubuf_t *gpubuf, uint8_t *moves, char *sequence,
+                      char *qstring);
+/* Wait for the gpubuf's decode in flight; returns its status (device-side status included). */
+int ofb_decode_wait(const openfish_gpubuf_t *gpubuf);
+int ofb_last_decode_ms(const openfish_gpubuf_t *gpubuf, float ms[4]);
+
+int ofb_rotary(void *x, const void *sin_t, const void *cos_t, int batch, int seqlen, int nheads,
+               int rotary_half, long long stride_batch, long long stride_seq,
+               long long stride_head);
+
+const char *ofb_error_text(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

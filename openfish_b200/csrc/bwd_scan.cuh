@@ -1,0 +1,10 @@
+// bwd_scan.cuh -- launcher of the backward scan kernel (see bwd_scan.cu).
+#pragma once
+#include <cuda_runtime.h>
+namespace ofx { struct Tables; }
+
+// scores_fp16: [T][N][>=4*ns] fp16, 16-byte aligned; bwd: [N][T+1][ns] fp32;
+// tables: device copy of ofx::Tables; status: device int raised on a bounded-wait timeout.
+cudaError_t of_launch_bwd_scan(const void *scores_fp16, float *bwd, int T, int N, int state_len,
+                               float stay, const ofx::Tables *tables, int *status,
+                               cudaStream_t stream);

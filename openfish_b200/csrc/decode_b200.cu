@@ -1,0 +1,270 @@
+// decode_b200.cu -- device buffers, stream and launch orchestration of the decode path.
+//
+// Replaces gpubuf_init_cuda / gpubuf_free_cuda / decode_cuda (src/decode_cuda.cu:11-212).
+// Differences in design: the caller-visible openfish_gpubuf_t sits at the start of a private
+// record that also owns a stream, timing events, the arithmetic tables and a page-locked
+// staging area; one decode is two kernel launches and one device-to-host copy, all stream
+// ordered, with a single host wait at the end (the reference launches five kernels and three
+// memsets with a device-wide synchronisation after each and copies with three blocking
+// pageable transfers).
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "backend.h"
+#include "bwd_scan.cuh"
+#include "exact_math.cuh"
+#include "fwd_beam.cuh"
+#include "of_device.cuh"
+#include "openfish_b200.h"
+#include "rotary.cuh"
+
+namespace {
+
+constexpr uint32_t kMagic = 0x0F15B200u;
+
+struct GpuBuf {
+    openfish_gpubuf_t pub;  // must stay first: the public pointer is the record's address
+    uint32_t magic;
+    int T, N, state_len, device;
+    cudaStream_t stream;
+    cudaEvent_t ev[4];
+    ofx::Tables *d_tables;
+    int *d_status;
+    unsigned char *d_results;  // moves | sequence | qstring, N*T bytes each
+    unsigned char *h_stage;    // page-locked, 3*N*T bytes + one status word
+    int *h_status;
+    // decode in flight
+    bool pending;
+    uint8_t *dst_moves;
+    char *dst_sequence, *dst_qstring;
+    bool via_stage;
+    float ms[4];
+};
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+#define CU(call)                                                                              \
+    do {                                                                                      \
+        cudaError_t e_ = (call);                                                              \
+        if (e_ != cudaSuccess)                                                                \
+            return fail(e_ == cudaErrorMemoryAllocation ? OPENFISH_B200_ERR_ALLOC             \
+                                                        : OPENFISH_B200_ERR_CUDA,             \
+                        "%s failed: %s", #call, cudaGetErrorString(e_));                      \
+    } while (0)
+
+GpuBuf *priv(const openfish_gpubuf_t *g) {
+    return reinterpret_cast<GpuBuf *>(const_cast<openfish_gpubuf_t *>(g));
+}
+
+bool host_is_pinned(const void *p) {
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return at.type == cudaMemoryTypeHost;
+}
+
+int destroy(GpuBuf *g) {
+    if (!g) return OPENFISH_B200_OK;
+    if (g->pending && g->stream) cudaStreamSynchronize(g->stream);
+    cudaFree(g->pub.bwd_NTC);
+    cudaFree(g->pub.post_NTC);
+    cudaFree(g->d_results);
+    cudaFree(g->pub.beam_vector);
+    cudaFree(g->pub.states);
+    cudaFree(g->pub.qual_data);
+    cudaFree(g->pub.base_probs);
+    cudaFree(g->pub.total_probs);
+    cudaFree(g->d_tables);
+    cudaFree(g->d_status);
+    if (g->h_stage) cudaFreeHost(g->h_stage);
+    for (int i = 0; i < 4; ++i)
+        if (g->ev[i]) cudaEventDestroy(g->ev[i]);
+    if (g->stream) cudaStreamDestroy(g->stream);
+    g->magic = 0;
+    free(g);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(OPENFISH_B200_ERR_CUDA, "releasing device buffers failed: %s", cudaGetErrorString(e));
+    return OPENFISH_B200_OK;
+}
+
+}  // namespace
+
+extern "C" const char *ofb_error_text(void) { return g_err; }
+
+extern "C" int ofb_gpubuf_create(int T, int N, int state_len, openfish_gpubuf_t **out) {
+    *out = nullptr;
+    GpuBuf *g = static_cast<GpuBuf *>(calloc(1, sizeof(GpuBuf)));
+    if (!g) return fail(OPENFISH_B200_ERR_ALLOC, "out of host memory");
+    g->T = T; g->N = N; g->state_len = state_len;
+    const size_t ns = (size_t)1 << (2 * state_len);
+    const size_t nt = (size_t)N * T;
+    const size_t tens = (size_t)N * (T + 1) * ns * sizeof(float);
+    int rc = [&]() -> int {
+        CU(cudaGetDevice(&g->device));
+        // a blocking stream: ordered after work the caller queued on the legacy default
+        // stream (where the reference runs), so freshly written scores are seen
+        CU(cudaStreamCreateWithFlags(&g->stream, cudaStreamDefault));
+        for (int i = 0; i < 4; ++i) CU(cudaEventCreate(&g->ev[i]));
+        // same ten buffers and sizes as the reference (src/decode_cuda.cu:22-45); the three
+        // result arrays share one allocation so that one copy brings them back
+        CU(cudaMalloc(&g->pub.bwd_NTC, tens));
+        CU(cudaMalloc(&g->pub.post_NTC, tens));
+        CU(cudaMalloc(&g->d_results, 3 * nt));
+        g->pub.moves = g->d_results;
+        g->pub.sequence = reinterpret_cast<char *>(g->d_results + nt);
+        g->pub.qstring = reinterpret_cast<char *>(g->d_results + 2 * nt);
+        CU(cudaMalloc(&g->pub.beam_vector, (size_t)8 * N * 32 * (T + 1)));
+        CU(cudaMalloc(&g->pub.states, sizeof(int32_t) * nt));
+        CU(cudaMalloc(&g->pub.qual_data, sizeof(float) * nt * 4));
+        CU(cudaMalloc(&g->pub.base_probs, sizeof(float) * nt));
+        CU(cudaMalloc(&g->pub.total_probs, sizeof(float) * nt));
+        CU(cudaMalloc(&g->d_tables, sizeof(ofx::Tables)));
+        CU(cudaMalloc(&g->d_status, sizeof(int)));
+        CU(cudaMallocHost(&g->h_stage, 3 * nt + 16));
+        g->h_status = reinterpret_cast<int *>(g->h_stage + ((3 * nt + 7) & ~(size_t)7));
+        ofx::Tables host_tables;
+        ofx::fill_tables(&host_tables);
+        CU(cudaMemcpy(g->d_tables, &host_tables, sizeof(host_tables), cudaMemcpyHostToDevice));
+        CU(cudaMemset(g->d_status, 0, sizeof(int)));
+        return OPENFISH_B200_OK;
+    }();
+    if (rc != OPENFISH_B200_OK) {
+        char keep[sizeof(g_err)];
+        memcpy(keep, g_err, sizeof(keep));
+        destroy(g);
+        memcpy(g_err, keep, sizeof(keep));
+        return rc;
+    }
+    g->magic = kMagic;
+    *out = &g->pub;
+    return OPENFISH_B200_OK;
+}
+
+extern "C" int ofb_gpubuf_destroy(openfish_gpubuf_t *gpubuf) {
+    if (!gpubuf) return OPENFISH_B200_OK;
+    GpuBuf *g = priv(gpubuf);
+    if (g->magic != kMagic) return fail(OPENFISH_B200_ERR_ARGUMENT, "gpubuf was not created by openfish_gpubuf_init");
+    return destroy(g);
+}
+
+extern "C" int ofb_gpubuf_check(const openfish_gpubuf_t *gpubuf, int T, int N, int state_len) {
+    if (!gpubuf) return fail(OPENFISH_B200_ERR_ARGUMENT, "gpubuf is NULL");
+    const GpuBuf *g = priv(gpubuf);
+    if (g->magic != kMagic) return fail(OPENFISH_B200_ERR_ARGUMENT, "gpubuf was not created by openfish_gpubuf_init");
+    if (g->T != T || g->N != N || g->state_len != state_len)
+        return fail(OPENFISH_B200_ERR_SHAPE, "gpubuf was sized for T=%d N=%d state_len=%d, decode asked for T=%d N=%d state_len=%d",
+                    g->T, g->N, g->state_len, T, N, state_len);
+    return OPENFISH_B200_OK;
+}
+
+extern "C" int ofb_decode_submit(int T, int N, int C, const void *scores, int state_len,
+                                 float beam_cut, float blank_score, float q_shift, float q_scale,
+                                 const openfish_gpubuf_t *gpubuf, uint8_t *moves, char *sequence,
+                                 char *qstring) {
+    GpuBuf *g = priv(gpubuf);
+    if (g->pending) return fail(OPENFISH_B200_ERR_ARGUMENT, "a decode is already in flight on this gpubuf");
+    int dev = -1;
+    CU(cudaGetDevice(&dev));
+    if (dev != g->device) return fail(OPENFISH_B200_ERR_ARGUMENT, "gpubuf belongs to device %d, current device is %d", g->device, dev);
+    const size_t nt = (size_t)N * T;
+
+    CU(cudaEventRecord(g->ev[0], g->stream));
+    CU(of_launch_bwd_scan(scores, g->pub.bwd_NTC, T, N, state_len, blank_score, g->d_tables,
+                          g->d_status, g->stream));
+    CU(cudaEventRecord(g->ev[1], g->stream));
+    OfFusedLaunch l;
+    l.scores_fp16 = scores;
+    l.bwd = g->pub.bwd_NTC;
+    l.post = g->pub.post_NTC;
+    l.bp = static_cast<unsigned char *>(g->pub.beam_vector);
+    l.moves = g->pub.moves;
+    l.sequence = g->pub.sequence;
+    l.qstring = g->pub.qstring;
+    l.states = static_cast<int *>(g->pub.states);
+    l.qual = g->pub.qual_data;
+    l.base_probs = g->pub.base_probs;
+    l.total_probs = g->pub.total_probs;
+    l.tables = g->d_tables;
+    l.status = g->d_status;
+    l.T = T; l.N = N; l.C = C; l.state_len = state_len;
+    l.stay = blank_score;
+    l.log_beam_cut = beam_cut > 0.0f ? logf(beam_cut) : 3.402823466e+38f;  // src/beam_search.c:135
+    l.q_shift = q_shift;
+    l.q_scale = q_scale;
+    CU(of_launch_fwd_beam(l, g->stream));
+    CU(cudaEventRecord(g->ev[2], g->stream));
+
+    // results: straight into page-locked caller memory, else through the staging area
+    g->via_stage = !(host_is_pinned(moves) && host_is_pinned(sequence) && host_is_pinned(qstring));
+    if (g->via_stage) {
+        CU(cudaMemcpyAsync(g->h_stage, g->d_results, 3 * nt, cudaMemcpyDeviceToHost, g->stream));
+    } else {
+        CU(cudaMemcpyAsync(moves, g->pub.moves, nt, cudaMemcpyDeviceToHost, g->stream));
+        CU(cudaMemcpyAsync(sequence, g->pub.sequence, nt, cudaMemcpyDeviceToHost, g->stream));
+        CU(cudaMemcpyAsync(qstring, g->pub.qstring, nt, cudaMemcpyDeviceToHost, g->stream));
+    }
+    CU(cudaMemcpyAsync(g->h_status, g->d_status, sizeof(int), cudaMemcpyDeviceToHost, g->stream));
+    CU(cudaEventRecord(g->ev[3], g->stream));
+    g->dst_moves = moves;
+    g->dst_sequence = sequence;
+    g->dst_qstring = qstring;
+    g->pending = true;
+    return OPENFISH_B200_OK;
+}
+
+extern "C" int ofb_decode_wait(const openfish_gpubuf_t *gpubuf) {
+    GpuBuf *g = priv(gpubuf);
+    if (!g->pending) return OPENFISH_B200_OK;
+    g->pending = false;
+    CU(cudaStreamSynchronize(g->stream));
+    const size_t nt = (size_t)g->N * g->T;
+    if (*g->h_status != ofd::kStatusOk) {
+        const int st = *g->h_status;
+        cudaMemsetAsync(g->d_status, 0, sizeof(int), g->stream);
+        return fail(OPENFISH_B200_ERR_DEVICE_WAIT, "decode kernel raised device status %d (an asynchronous copy did not complete in time)", st);
+    }
+    if (g->via_stage) {
+        memcpy(g->dst_moves, g->h_stage, nt);
+        memcpy(g->dst_sequence, g->h_stage + nt, nt);
+        memcpy(g->dst_qstring, g->h_stage + 2 * nt, nt);
+    }
+    cudaEventElapsedTime(&g->ms[0], g->ev[0], g->ev[1]);
+    cudaEventElapsedTime(&g->ms[1], g->ev[1], g->ev[2]);
+    cudaEventElapsedTime(&g->ms[2], g->ev[2], g->ev[3]);
+    cudaEventElapsedTime(&g->ms[3], g->ev[0], g->ev[3]);
+    return OPENFISH_B200_OK;
+}
+
+extern "C" int ofb_last_decode_ms(const openfish_gpubuf_t *gpubuf, float ms[4]) {
+    const GpuBuf *g = priv(gpubuf);
+    for (int i = 0; i < 4; ++i) ms[i] = g->ms[i];
+    return OPENFISH_B200_OK;
+}
+
+extern "C" int ofb_rotary(void *x, const void *sin_t, const void *cos_t, int batch, int seqlen,
+                          int nheads, int rotary_half, long long stride_batch,
+                          long long stride_seq, long long stride_head) {
+    int dev = 0, sms = 0;
+    CU(cudaGetDevice(&dev));
+    CU(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    // the reference launches on the legacy default stream and waits for the device
+    // (src/nn_cuda.cu:27-39); same stream here, and a wait on that stream only
+    CU(of_launch_rotary(x, sin_t, cos_t, batch, seqlen, nheads, rotary_half, stride_batch,
+                        stride_seq, stride_head, sms, 0));
+    CU(cudaStreamSynchronize(0));
+    return OPENFISH_B200_OK;
+}

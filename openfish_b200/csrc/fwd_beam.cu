@@ -1,0 +1,670 @@
+// fwd_beam.cu -- forward scan + posterior, beam search, traceback, per-base quality and
+// sequence/qstring generation for one chunk per block, fused in one sm_100a kernel.
+//
+// Replaces the reference kernels fwd_post_scan (src/scan_cuda.cu:59-199), beam_search
+// (src/beam_search_cuda.cu:139-528), compute_qual_data (:530-605) and generate_sequence
+// (:52-121).  The beam search follows the reference's CPU routine beam_search_cpu
+// (src/beam_search.c:117-497) -- including its bisection of the pruning threshold, which the
+// reference's CUDA kernel lacks -- because output parity is defined against the CPU decoder.
+//
+// Roles inside a block (one chunk):
+//   scan warps   ns/4 threads, four consecutive states each: forward recursion in shared memory
+//                (one named barrier per timestep) and the posterior softmax of fwd+bwd.  The
+//                softmax needs no per-row maximum: the log partition function is the same for
+//                every row, so one offset taken from row 0 keeps every exponent in range; the
+//                row sum is reduced across warps and applied one timestep late.
+//   beam warp    lane = beam slot (width <= 32).  Everything is warp-synchronous: candidate
+//                scores, duplicate-prefix merges (CRC32C hashes; a stay merges with the step
+//                whose parent hash equals the stay's hash run backwards through the CRC),
+//                maximum, threshold bisection by population counts, order-preserving
+//                compaction by ballots.  One packed back-pointer byte per slot and timestep
+//                goes to HBM (prev slot 5 bits | stay 1 bit | base 2 bits).
+//   copy warp    one lane issues 1-D bulk asynchronous copies (no multicast) of score row t and
+//                backward row t into a ring; both consumers release a ring slot through an
+//                mbarrier.  Scores are read from HBM once for both consumers.
+// After the last timestep the block walks the back-pointers (staged through shared memory in
+// windows), rebuilds the k-mer of every path element from the emitted bases, gathers the
+// posterior of each path k-mer and its shifted neighbours, and emits moves, sequence and
+// qstring, zero-filling the unused tail of each row.
+#include <float.h>
+
+#include "exact_math.cuh"
+#include "fwd_beam.cuh"
+#include "of_device.cuh"
+
+namespace {
+
+constexpr int kBeam = 32;
+constexpr int kWin = 256;  // traceback window, timesteps
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float lg2_approx(float x) {
+    float y;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+// Five-term log-sum-exp in fast fp32 (the forward scores only feed the posterior, which is
+// compared within a tolerance, not bit for bit).
+__device__ __forceinline__ float lse5_fast(float a, float b, float c, float d, float e) {
+    const float m = fmaxf(fmaxf(fmaxf(a, b), fmaxf(c, d)), e);
+    const float s = ex2_approx((a - m) * kLog2e) + ex2_approx((b - m) * kLog2e) +
+                    ex2_approx((c - m) * kLog2e) + ex2_approx((d - m) * kLog2e) +
+                    ex2_approx((e - m) * kLog2e);
+    return fmaf(lg2_approx(s), kLn2, m);
+}
+
+__device__ __forceinline__ float half_bits_to_float(uint32_t w, int odd) {
+    return __half2float(__ushort_as_half((unsigned short)(odd ? (w >> 16) : (w & 0xffffu))));
+}
+
+// CRC32C over two input bits, table form of src/beam_search.c:103-115:
+// crc' = (crc >> 2) ^ tab[(crc ^ bits) & 3], tab = {0, 0x417B1DBC, 0x82F63B78, 0xC38D26C4}.
+__device__ __forceinline__ uint32_t crc_tab2(uint32_t x) {
+    return ((x & 1u) ? 0x417B1DBCu : 0u) ^ ((x & 2u) ? 0x82F63B78u : 0u);
+}
+__device__ __forceinline__ uint32_t crc_step2(uint32_t crc, uint32_t bits) {
+    return (crc >> 2) ^ crc_tab2((crc ^ bits) & 3u);
+}
+// The update is a bijection for fixed input bits (the table's top two bits equal its index),
+// so the parent hash that would step to `crc` by appending `bits` is unique.
+__device__ __forceinline__ uint32_t crc_unstep2(uint32_t crc, uint32_t bits) {
+    const uint32_t idx = crc >> 30;
+    return ((crc ^ crc_tab2(idx)) << 2) | (idx ^ bits);
+}
+__device__ __forceinline__ uint32_t crc32c_bits(uint32_t crc, uint32_t v, int n) {
+    for (int i = 0; i < n; ++i) {
+        const uint32_t b = (v ^ crc) & 1u;
+        crc >>= 1;
+        if (b) crc ^= 0x82f63b78u;
+        v >>= 1;
+    }
+    return crc;
+}
+
+template <int NS, int RING>
+struct FusedSmem {
+    static constexpr int kScoreRow = NS * 8;  // bytes of one fp16 score row
+    static constexpr int kBwdRow = NS * 4;    // bytes of one fp32 backward row
+    alignas(16) float alpha[2][NS];
+    float psum[2][8];
+    float red[8];
+    alignas(16) uint4 rec[kBeam];
+    alignas(16) float cstep[kBeam * 4];
+    uint32_t bloom[128];
+    int init_state[kBeam];
+    double exp2_j[ofx::kExpTab];
+    double rcp_c[ofx::kLogTab];
+    double log_c[ofx::kLogTab];
+    alignas(8) uint64_t full[RING];
+    alignas(8) uint64_t empty[RING];
+    int abort_flag;
+    int part[352];  // block-scan partials of the tail phase
+    // rings last: the tail phase reuses them (and whatever dynamic shared memory follows)
+    alignas(128) unsigned char score_ring[RING][kScoreRow];
+    alignas(128) unsigned char bwd_ring[RING][kBwdRow];
+};
+
+struct FusedArgs {
+    const __half *scores;  // [T][N][C] fp16
+    const float *bwd;      // [N][T+1][ns]
+    float *post;           // [N][T+1][ns]
+    unsigned char *bp;     // [N][T+1][32] packed back-pointers
+    uint8_t *moves;        // [N][T]
+    char *sequence;        // [N][T]
+    char *qstring;         // [N][T]
+    int *states;           // [N][T]   base of each path element
+    float *qual;           // [N][T][4]
+    float *base_probs;     // [N][T]
+    float *total_probs;    // [N][T]
+    const ofx::Tables *tables;
+    int *status;
+    int T, N, C;
+    float stay, log_beam_cut, q_shift, q_scale;
+};
+
+template <int NS, int RING>
+__global__ void __launch_bounds__((NS / 4 < 32 ? 32 : NS / 4) + 64)
+fwd_beam_kernel(const FusedArgs a) {
+    constexpr int BITS = (NS == 64) ? 6 : (NS == 256 ? 8 : 10);
+    constexpr int SL = BITS / 2;
+    constexpr int MSB = NS / 4;
+    constexpr int TPC = NS / 4;                 // scan threads that own states
+    constexpr int TPAD = TPC < 32 ? 32 : TPC;   // scan threads including idle lanes
+    constexpr int NFW = TPAD / 32;              // scan warps
+    constexpr int NT = TPAD + 64;
+    using Smem = FusedSmem<NS, RING>;
+    extern __shared__ unsigned char smem_raw[];
+    Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const int chunk = blockIdx.x;
+    const int T = a.T, N = a.N;
+    const bool own_beam_ring = a.C != NS * 4;  // beam search strides timesteps by N*C
+    // the beam search's own ring, when it has one, sits in dynamic shared memory behind the struct
+    unsigned char *beam_ring =
+        own_beam_ring ? reinterpret_cast<unsigned char *>(&sm) + sizeof(Smem) : &sm.score_ring[0][0];
+
+    for (int i = tid; i < ofx::kExpTab; i += NT) sm.exp2_j[i] = a.tables->exp2_j[i];
+    for (int i = tid; i < ofx::kLogTab; i += NT) {
+        sm.rcp_c[i] = a.tables->rcp_c[i];
+        sm.log_c[i] = a.tables->log_c[i];
+    }
+    for (int i = tid; i < 128; i += NT) sm.bloom[i] = 0;
+    if (tid == 0) {
+        sm.abort_flag = 0;
+        for (int r = 0; r < RING; ++r) {
+            ofd::mbar_init(&sm.full[r], 1);
+            ofd::mbar_init(&sm.empty[r], 2);
+        }
+        ofd::mbar_fence_init();
+    }
+    __syncthreads();
+
+    const float *bwd_chunk = a.bwd + (size_t)chunk * (size_t)(T + 1) * NS;
+    float *post_chunk = a.post + (size_t)chunk * (size_t)(T + 1) * NS;
+    unsigned char *bp_chunk = a.bp + (size_t)chunk * (size_t)(T + 1) * kBeam;
+
+    if (warp == NFW + 1) {
+        // ------------------------------------------------------------------ copy warp
+        if (lane == 0) {
+            const __half *scan_scores = a.scores + (size_t)chunk * NS * 4;  // scan addressing
+            const size_t scan_stride = (size_t)N * NS * 4;
+            const size_t beam_stride = (size_t)N * a.C;
+            for (int t = 0; t <= T; ++t) {
+                const int slot = t % RING;
+                if (t >= RING)
+                    ofd::mbar_wait_bounded(&sm.empty[slot], (uint32_t)(t / RING - 1) & 1u,
+                                           &sm.abort_flag, a.status);
+                if (sm.abort_flag) break;
+                uint32_t bytes = Smem::kBwdRow;
+                if (t < T) bytes += Smem::kScoreRow * (own_beam_ring ? 2 : 1);
+                ofd::mbar_arrive_expect_tx(&sm.full[slot], bytes);
+                ofd::bulk_g2s(sm.bwd_ring[slot], bwd_chunk + (size_t)t * NS, Smem::kBwdRow,
+                              &sm.full[slot]);
+                if (t < T) {
+                    ofd::bulk_g2s(sm.score_ring[slot], scan_scores + scan_stride * t,
+                                  Smem::kScoreRow, &sm.full[slot]);
+                    if (own_beam_ring)
+                        ofd::bulk_g2s(beam_ring + (size_t)slot * Smem::kScoreRow,
+                                      scan_scores + beam_stride * t, Smem::kScoreRow,
+                                      &sm.full[slot]);
+                }
+            }
+        }
+    } else if (warp < NFW) {
+        // ------------------------------------------------------------------ scan warps
+        const int j = tid;
+        const bool act = j < TPC;
+        const int sw = (j >> 2) & 1;
+        if (act) *reinterpret_cast<float4 *>(&sm.alpha[0][4 * j]) = make_float4(0.f, 0.f, 0.f, 0.f);
+        // softmax offset: maximum of fwd+bwd at row 0 (= bwd row 0, fwd is zero there)
+        ofd::mbar_wait_bounded(&sm.full[0], 0, &sm.abort_flag, a.status);
+        float m0 = -FLT_MAX;
+        if (act) {
+            const float4 b0 = *reinterpret_cast<const float4 *>(sm.bwd_ring[0] + 16 * j);
+            m0 = fmaxf(fmaxf(b0.x, b0.y), fmaxf(b0.z, b0.w));
+        }
+        m0 = ofd::warp_max(m0);
+        if (lane == 0) sm.red[warp] = m0;
+        ofd::named_bar_sync(1, TPAD);
+        m0 = sm.red[0];
+#pragma unroll
+        for (int w = 1; w < NFW; ++w) m0 = fmaxf(m0, sm.red[w]);
+
+        float e_prev[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int t = 0; t <= T; ++t) {
+            const int slot = t % RING;
+            ofd::mbar_wait_bounded(&sm.full[slot], (uint32_t)(t / RING) & 1u, &sm.abort_flag,
+                                   a.status);
+            float nw[4] = {0.f, 0.f, 0.f, 0.f};
+            float e[4] = {0.f, 0.f, 0.f, 0.f};
+            if (act) {
+                const float *ain = sm.alpha[t & 1];
+                const float4 own = *reinterpret_cast<const float4 *>(ain + 4 * j);
+                const float p0 = ain[j], p1 = ain[j + MSB], p2 = ain[j + 2 * MSB], p3 = ain[j + 3 * MSB];
+                const float4 bw = *reinterpret_cast<const float4 *>(sm.bwd_ring[slot] + 16 * j);
+                uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
+                if (t < T) {
+                    const unsigned char *row = sm.score_ring[slot] + 32 * j;
+                    const uint4 q0 = *reinterpret_cast<const uint4 *>(row + 16 * sw);
+                    const uint4 q1 = *reinterpret_cast<const uint4 *>(row + 16 * (1 - sw));
+                    lo = sw ? q1 : q0;
+                    hi = sw ? q0 : q1;
+                }
+                const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+                const float ow[4] = {own.x, own.y, own.z, own.w};
+                const float bv[4] = {bw.x, bw.y, bw.z, bw.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    // state 4j+k: predecessors j + b*ns/4, score columns 4(4j+k) + b
+                    nw[k] = lse5_fast(ow[k] + a.stay, p0 + half_bits_to_float(w[2 * k], 0),
+                                      p1 + half_bits_to_float(w[2 * k], 1),
+                                      p2 + half_bits_to_float(w[2 * k + 1], 0),
+                                      p3 + half_bits_to_float(w[2 * k + 1], 1));
+                    e[k] = ex2_approx(((ow[k] + bv[k]) - m0) * kLog2e);
+                }
+                *reinterpret_cast<float4 *>(&sm.alpha[(t & 1) ^ 1][4 * j]) =
+                    make_float4(nw[0], nw[1], nw[2], nw[3]);
+            }
+            float part = (e[0] + e[1]) + (e[2] + e[3]);
+#pragma unroll
+            for (int o = 16; o; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+            if (lane == 0) sm.psum[t & 1][warp] = part;
+            if (t > 0 && act) {
+                float s = sm.psum[(t - 1) & 1][0];
+#pragma unroll
+                for (int w = 1; w < NFW; ++w) s += sm.psum[(t - 1) & 1][w];
+                const float inv = 1.0f / s;
+                *reinterpret_cast<float4 *>(post_chunk + (size_t)(t - 1) * NS + 4 * j) =
+                    make_float4(e_prev[0] * inv, e_prev[1] * inv, e_prev[2] * inv, e_prev[3] * inv);
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) e_prev[k] = e[k];
+            ofd::named_bar_sync(1, TPAD);
+            if (tid == 0) ofd::mbar_arrive(&sm.empty[slot]);
+        }
+        if (act) {
+            float s = sm.psum[T & 1][0];
+#pragma unroll
+            for (int w = 1; w < NFW; ++w) s += sm.psum[T & 1][w];
+            const float inv = 1.0f / s;
+            *reinterpret_cast<float4 *>(post_chunk + (size_t)T * NS + 4 * j) =
+                make_float4(e_prev[0] * inv, e_prev[1] * inv, e_prev[2] * inv, e_prev[3] * inv);
+        }
+    } else {
+        // ------------------------------------------------------------------ beam warp
+        const ofx::TabRef tr = {sm.exp2_j, 1, sm.rcp_c, sm.log_c};
+        const uint32_t lt_mask = (1u << lane) - 1u;
+        ofd::mbar_wait_bounded(&sm.full[0], 0, &sm.abort_flag, a.status);
+        // initial beam: first <= 32 states, in state order, reaching the 32nd largest bwd[0]
+        // (src/beam_search.c:151-175).  Radix-select the 32nd largest key bit by bit.
+        {
+            const float *b0 = reinterpret_cast<const float *>(sm.bwd_ring[0]);
+            constexpr int PER = NS / 32;
+            uint32_t key[PER];
+#pragma unroll
+            for (int i = 0; i < PER; ++i)
+                key[i] = (uint32_t)ofd::float_order_key(b0[lane + 32 * i]) ^ 0x80000000u;
+            uint32_t thr = 0;
+            for (int bit = 31; bit >= 0; --bit) {
+                const uint32_t cand = thr | (1u << bit);
+                int c = 0;
+#pragma unroll
+                for (int i = 0; i < PER; ++i) c += key[i] >= cand;
+                c = __reduce_add_sync(0xffffffffu, c);
+                if (c >= kBeam) thr = cand;
+            }
+            int filled = 0;
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                const bool f = key[i] >= thr;
+                const uint32_t bal = __ballot_sync(0xffffffffu, f);
+                const int pos = filled + __popc(bal & lt_mask);
+                if (f && pos < kBeam) sm.init_state[pos] = lane + 32 * i;
+                filled += __popc(bal);
+            }
+            __syncwarp();
+        }
+        int state = sm.init_state[lane];
+        uint32_t hash = crc32c_bits(0x12345678u, (uint32_t)state, 32);
+        float score = 0.f;
+        int W = kBeam;
+        bp_chunk[lane] = (unsigned char)((state & 3) << 6);
+
+        for (int t = 0; t < T; ++t) {
+            const int slot_a = t % RING, slot_b = (t + 1) % RING;
+            ofd::mbar_wait_bounded(&sm.full[slot_a], (uint32_t)(t / RING) & 1u, &sm.abort_flag, a.status);
+            ofd::mbar_wait_bounded(&sm.full[slot_b], (uint32_t)((t + 1) / RING) & 1u, &sm.abort_flag, a.status);
+            const __half *srow = reinterpret_cast<const __half *>(beam_ring + (size_t)slot_a * Smem::kScoreRow);
+            const float *brow = reinterpret_cast<const float *>(sm.bwd_ring[slot_b]);
+            const bool act = lane < W;
+            const int q = state & (MSB - 1);
+            const int top = state >> (BITS - 2);
+            const uint32_t b_own = (uint32_t)state & 3u;
+
+            // candidates: 4 steps (state' = 4q + b, column 16q + 4b + top) and the stay
+            float c0, c1, c2, c3, c4;
+            if (act) {
+                const float4 bw = *reinterpret_cast<const float4 *>(brow + 4 * q);
+                const __half *sp = srow + 16 * q + top;
+                c0 = __fadd_rn(__fadd_rn(score, __half2float(sp[0])), bw.x);
+                c1 = __fadd_rn(__fadd_rn(score, __half2float(sp[4])), bw.y);
+                c2 = __fadd_rn(__fadd_rn(score, __half2float(sp[8])), bw.z);
+                c3 = __fadd_rn(__fadd_rn(score, __half2float(sp[12])), bw.w);
+                c4 = __fadd_rn(__fadd_rn(score, a.stay), brow[state]);
+            } else {
+                c0 = c1 = c2 = c3 = c4 = -INFINITY;
+            }
+
+            // duplicate-prefix merges (src/beam_search.c:281-316)
+            const uint32_t need = crc_unstep2(hash, b_own);
+            if (act) atomicOr(&sm.bloom[(hash >> 5) & 127u], 1u << (hash & 31u));
+            __syncwarp();
+            const bool hit = act && ((sm.bloom[(need >> 5) & 127u] >> (need & 31u)) & 1u);
+            const uint32_t pot = __ballot_sync(0xffffffffu, hit);
+            __syncwarp();
+            if (act) sm.bloom[(hash >> 5) & 127u] = 0u;
+            if (pot) {
+                int mate = -1;
+                bool conflict = false;
+                unsigned long long claimed01 = 0ull, claimed23 = 0ull;
+                for (uint32_t rem = pot; rem; rem &= rem - 1) {
+                    const int i = __ffs(rem) - 1;
+                    const uint32_t need_i = __shfl_sync(0xffffffffu, need, i);
+                    const uint32_t b_i = __shfl_sync(0xffffffffu, b_own, i);
+                    const uint32_t m = __ballot_sync(0xffffffffu, act && hash == need_i);
+                    if (m) {
+                        if (m & (m - 1)) conflict = true;
+                        const int jj = __ffs(m) - 1;
+                        const unsigned long long bitpos = 1ull << (((b_i & 1u) << 5) + jj);
+                        unsigned long long &cl = (b_i & 2u) ? claimed23 : claimed01;
+                        if (cl & bitpos) conflict = true;
+                        cl |= bitpos;
+                        if (lane == i) mate = jj;
+                    }
+                }
+                if (__any_sync(0xffffffffu, mate >= 0)) {
+                    *reinterpret_cast<float4 *>(&sm.cstep[4 * lane]) = make_float4(c0, c1, c2, c3);
+                    if (conflict) sm.rec[lane] = make_uint4(hash, b_own, __float_as_uint(c4), 0u);
+                    __syncwarp();
+                    if (!conflict) {
+                        // every stay has at most one partner and no step has two: the folds
+                        // are independent, so all of them run at once
+                        if (mate >= 0) {
+                            const float x = c4, y = sm.cstep[4 * mate + b_own];
+                            const float f = ofx::fold2_exact(x, y, tr);
+                            if (x > y) {
+                                c4 = f;
+                                sm.cstep[4 * mate + b_own] = -FLT_MAX;
+                            } else {
+                                sm.cstep[4 * mate + b_own] = f;
+                                c4 = -FLT_MAX;
+                            }
+                        }
+                        __syncwarp();
+                    } else {
+                        // repeated hashes inside the beam (CRC collisions): replay the
+                        // reference's nested loop, stay-major then slot-minor, on one lane
+                        if (lane == 0) {
+                            for (int i = 0; i < W; ++i) {
+                                const uint32_t h_i = sm.rec[i].x, b_i = sm.rec[i].y;
+                                for (int jj = 0; jj < W; ++jj) {
+                                    if (h_i != crc_step2(sm.rec[jj].x, b_i)) continue;
+                                    const float x = __uint_as_float(sm.rec[i].z);
+                                    const float y = sm.cstep[4 * jj + b_i];
+                                    const float f = ofx::fold2_exact(x, y, tr);
+                                    if (x > y) {
+                                        sm.rec[i].z = __float_as_uint(f);
+                                        sm.cstep[4 * jj + b_i] = -FLT_MAX;
+                                    } else {
+                                        sm.cstep[4 * jj + b_i] = f;
+                                        sm.rec[i].z = __float_as_uint(-FLT_MAX);
+                                    }
+                                }
+                            }
+                        }
+                        __syncwarp();
+                        if (act) c4 = __uint_as_float(sm.rec[lane].z);
+                    }
+                    const float4 r = *reinterpret_cast<const float4 *>(&sm.cstep[4 * lane]);
+                    c0 = r.x; c1 = r.y; c2 = r.z; c3 = r.w;
+                }
+            }
+
+            // pruning threshold (src/beam_search.c:320-381)
+            const float lmax = fmaxf(fmaxf(fmaxf(c0, c1), fmaxf(c2, c3)), c4);
+            const float best = ofd::warp_max(lmax);
+            float cut = __fsub_rn(best, a.log_beam_cut);
+            auto count_at_least = [&](float th) {
+                const int n = (c0 >= th) + (c1 >= th) + (c2 >= th) + (c3 >= th) + (c4 >= th);
+                return __reduce_add_sync(0xffffffffu, n);
+            };
+            int kept = count_at_least(cut);
+            if (kept > kBeam) {
+                float lo = cut, hi = best;
+                int guesses = 1;
+                while ((kept > kBeam || kept < 25) && guesses < 10) {
+                    if (kept > kBeam) {
+                        lo = cut;
+                        cut = __fmul_rn(__fadd_rn(cut, hi), 0.5f);
+                    } else {
+                        hi = cut;
+                        cut = __fmul_rn(__fadd_rn(cut, lo), 0.5f);
+                    }
+                    kept = count_at_least(cut);
+                    ++guesses;
+                }
+                if (guesses == 10) {
+                    cut = hi;
+                    kept = count_at_least(cut);
+                }
+                kept = min(kept, kBeam);
+            }
+
+            // survivors keep candidate order: steps (slot-major, base-minor), then stays
+            const bool f0 = c0 >= cut, f1 = c1 >= cut, f2 = c2 >= cut, f3 = c3 >= cut, f4 = c4 >= cut;
+            const uint32_t B0 = __ballot_sync(0xffffffffu, f0), B1 = __ballot_sync(0xffffffffu, f1);
+            const uint32_t B2 = __ballot_sync(0xffffffffu, f2), B3 = __ballot_sync(0xffffffffu, f3);
+            const uint32_t B4 = __ballot_sync(0xffffffffu, f4);
+            int p = __popc(B0 & lt_mask) + __popc(B1 & lt_mask) + __popc(B2 & lt_mask) + __popc(B3 & lt_mask);
+            const int nsteps = __popc(B0) + __popc(B1) + __popc(B2) + __popc(B3);
+            const int base_state = (state << 2) & (NS - 1);
+            if (f0) { if (p < kBeam) sm.rec[p] = make_uint4(crc_step2(hash, 0), base_state | 0, __float_as_uint(c0), lane | (0 << 6)); ++p; }
+            if (f1) { if (p < kBeam) sm.rec[p] = make_uint4(crc_step2(hash, 1), base_state | 1, __float_as_uint(c1), lane | (1 << 6)); ++p; }
+            if (f2) { if (p < kBeam) sm.rec[p] = make_uint4(crc_step2(hash, 2), base_state | 2, __float_as_uint(c2), lane | (2 << 6)); ++p; }
+            if (f3) { if (p < kBeam) sm.rec[p] = make_uint4(crc_step2(hash, 3), base_state | 3, __float_as_uint(c3), lane | (3 << 6)); ++p; }
+            const int ps = nsteps + __popc(B4 & lt_mask);
+            if (f4 && ps < kBeam) sm.rec[ps] = make_uint4(hash, state, __float_as_uint(c4), lane | 32 | (b_own << 6));
+            __syncwarp();
+            W = kept;
+            uint32_t meta = 0;
+            if (lane < W) {
+                const uint4 r = sm.rec[lane];
+                hash = r.x;
+                state = (int)r.y;
+                score = __uint_as_float(r.z);
+                meta = r.w;
+            }
+            __syncwarp();
+            if (t == T - 1) {
+                // best survivor swaps into slot 0 (src/beam_search.c:398-414)
+                const float sc = lane < W ? score : -INFINITY;
+                const float top_s = ofd::warp_max(sc);
+                const uint32_t eq = __ballot_sync(0xffffffffu, lane < W && sc == top_s && sc > -FLT_MAX);
+                const int at = eq ? __ffs(eq) - 1 : 0;
+                const uint32_t h0 = __shfl_sync(0xffffffffu, hash, 0), ha = __shfl_sync(0xffffffffu, hash, at);
+                const int s0 = __shfl_sync(0xffffffffu, state, 0), sa = __shfl_sync(0xffffffffu, state, at);
+                const float v0 = __shfl_sync(0xffffffffu, score, 0), va = __shfl_sync(0xffffffffu, score, at);
+                const uint32_t m0_ = __shfl_sync(0xffffffffu, meta, 0), ma = __shfl_sync(0xffffffffu, meta, at);
+                if (lane == at) { hash = h0; state = s0; score = v0; meta = m0_; }
+                if (lane == 0) { hash = ha; state = sa; score = va; meta = ma; }
+            }
+            if (lane < W) score = __fsub_rn(score, brow[state]);
+            bp_chunk[(size_t)(t + 1) * kBeam + lane] = (unsigned char)meta;
+            __syncwarp();
+            if (lane == 0) ofd::mbar_arrive(&sm.empty[slot_a]);
+        }
+    }
+
+    // ---------------------------------------------------------------------- tail, whole block
+    __syncthreads();
+    // arrays laid over the rings (and the dynamic shared memory behind them)
+    unsigned char *tail = sm.score_ring[0];
+    const int Tp = (T + 16) & ~15;
+    unsigned char *win = tail;                          // kWin * 32 bytes
+    unsigned char *path = win + kWin * kBeam;           // [T+1] packed back-pointer of the path
+    unsigned char *ext = path + Tp;                     // [SL + T] initial k-mer bases then steps
+    unsigned short *cnt = reinterpret_cast<unsigned short *>(ext + Tp + 16);  // [T+1] steps so far
+    float *qp = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(cnt) + 2 * Tp);  // [T]
+
+    // traceback from slot 0 of the last row (src/beam_search.c:430-438), window by window
+    int at = 0;
+    for (int hi_r = T; hi_r >= 1; hi_r -= kWin) {
+        const int lo_r = max(1, hi_r - kWin + 1);
+        const int n16 = (hi_r - lo_r + 1) * 2;  // 16-byte pieces
+        const uint4 *src = reinterpret_cast<const uint4 *>(bp_chunk + (size_t)lo_r * kBeam);
+        for (int i = tid; i < n16; i += NT) reinterpret_cast<uint4 *>(win)[i] = __ldcg(src + i);
+        __syncthreads();
+        if (tid == 0) {
+            for (int r = hi_r; r >= lo_r; --r) {
+                const unsigned char b = win[(r - lo_r) * kBeam + at];
+                path[r] = b;
+                at = b & 31;
+            }
+        }
+        __syncthreads();
+    }
+    if (tid == 0) {
+        const int st0 = sm.init_state[at];
+#pragma unroll
+        for (int i = 0; i < SL; ++i) ext[i] = (unsigned char)((st0 >> (2 * (SL - 1 - i))) & 3);
+    }
+    __syncthreads();
+
+    // running count of true steps along the path, and the stepped bases in order
+    const int seg = (T + NT - 1) / NT;
+    const int r_lo = 1 + tid * seg, r_hi = min(T, r_lo + seg - 1);
+    int local = 0;
+    for (int r = r_lo; r <= r_hi; ++r) local += !((path[r] >> 5) & 1);
+    sm.part[tid] = local;
+    __syncthreads();
+    int run = 0;
+    for (int i = 0; i < tid; ++i) run += sm.part[i];
+    for (int r = r_lo; r <= r_hi; ++r) {
+        const unsigned char b = path[r];
+        if (!((b >> 5) & 1)) {
+            ext[SL + run] = b >> 6;
+            ++run;
+        }
+        cnt[r] = (unsigned short)run;
+    }
+    if (tid == 0) cnt[0] = 0;
+    __syncthreads();
+
+    // per-timestep quality (src/beam_search.c:441-496)
+    const size_t ct = (size_t)chunk * T;
+    for (int t = tid; t < T; t += NT) {
+        const int r = t + 1;
+        const int c = cnt[r];
+        int st = 0;
+#pragma unroll
+        for (int i = 0; i < SL; ++i) st = (st << 2) | ext[c + i];
+        const int base = st & 3;
+        const float *pr = post_chunk + (size_t)r * NS;
+        float prob = __ldcg(pr + st);
+        int nb[8];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            nb[2 * b] = (st >> 2) + MSB * b;
+            nb[2 * b + 1] = ((st << 2) & (NS - 1)) + b;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            bool fresh = nb[k] != st;
+#pragma unroll
+            for (int m = 0; m < k; ++m) fresh = fresh && (nb[m] != nb[k]);
+            if (fresh) prob = __fadd_rn(prob, __ldcg(pr + nb[k]));
+        }
+        prob = prob > 1.0f ? 1.0f : (prob < 0.0f ? 0.0f : prob);
+        prob = powf(prob, 0.4f);
+        const float other = __fdiv_rn(__fsub_rn(1.0f, prob), 3.0f);
+        qp[t] = prob;
+        *reinterpret_cast<float4 *>(a.qual + (ct + t) * 4) =
+            make_float4(base == 0 ? prob : other, base == 1 ? prob : other,
+                        base == 2 ? prob : other, base == 3 ? prob : other);
+        a.states[ct + t] = base;
+        a.moves[ct + t] = (uint8_t)((t == 0) ? 1 : !((path[r] >> 5) & 1));
+    }
+    __syncthreads();
+
+    // bases and quality string (src/beam_search.c:49-99).  Position of timestep t =
+    // (number of moves up to and including t) - 1; move 0 is forced.
+    const int forced = (T > 0 && ((path[1] >> 5) & 1)) ? 1 : 0;
+    const int seq_len = T > 0 ? cnt[T] + forced : 0;
+    for (int t = tid; t < T; t += NT) {
+        const bool starts = (t == 0) || !((path[t + 1] >> 5) & 1);
+        if (!starts) continue;
+        const int pos = cnt[t + 1] + forced - 1;
+        const int b_emit = path[t + 1] >> 6;
+        float bsum = 0.f, tsum = 0.f;
+        for (int u = t; u < T; ++u) {
+            if (u > t && !((path[u + 1] >> 5) & 1)) break;
+            const int b = path[u + 1] >> 6;
+            const float pq = qp[u];
+            const float other = __fdiv_rn(__fsub_rn(1.0f, pq), 3.0f);
+            bsum = __fadd_rn(bsum, pq);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) tsum = __fadd_rn(tsum, k == b ? pq : other);
+        }
+        float v = __fsub_rn(1.0f, __fdiv_rn(bsum, tsum));
+        v = __fmul_rn(-10.0f, log10f(v));
+        float qs = __fadd_rn(__fmul_rn(v, a.q_scale), a.q_shift);
+        if (qs > 50.0f) qs = 50.0f;
+        if (qs < 1.0f) qs = 1.0f;
+        a.base_probs[ct + pos] = v;
+        a.total_probs[ct + pos] = tsum;
+        a.sequence[ct + pos] = "ACGT"[b_emit];
+        a.qstring[ct + pos] = (char)(33.5f + qs);
+    }
+    for (int i = seq_len + tid; i < T; i += NT) {
+        a.sequence[ct + i] = 0;
+        a.qstring[ct + i] = 0;
+        a.base_probs[ct + i] = 0.f;
+        a.total_probs[ct + i] = 0.f;
+    }
+}
+
+}  // namespace
+
+namespace {
+
+template <int NS, int RING>
+cudaError_t launch(const OfFusedLaunch &l, cudaStream_t stream) {
+    using Smem = FusedSmem<NS, RING>;
+    const int Tp = (l.T + 16) & ~15;
+    const size_t ring_bytes = (size_t)RING * (Smem::kScoreRow + Smem::kBwdRow);
+    const size_t extra = (l.C != NS * 4) ? (size_t)RING * Smem::kScoreRow : 0;
+    const size_t tail = (size_t)kWin * kBeam + 8 * (size_t)Tp + 64;
+    size_t bytes = sizeof(Smem) + extra + 128;
+    if (tail > ring_bytes + extra) bytes += tail - (ring_bytes + extra);
+    if (bytes > 227 * 1024) return cudaErrorInvalidValue;
+    auto kern = fwd_beam_kernel<NS, RING>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) return e;
+    FusedArgs a;
+    a.scores = static_cast<const __half *>(l.scores_fp16);
+    a.bwd = l.bwd; a.post = l.post; a.bp = l.bp; a.moves = l.moves; a.sequence = l.sequence;
+    a.qstring = l.qstring; a.states = l.states; a.qual = l.qual; a.base_probs = l.base_probs;
+    a.total_probs = l.total_probs; a.tables = l.tables; a.status = l.status;
+    a.T = l.T; a.N = l.N; a.C = l.C; a.stay = l.stay; a.log_beam_cut = l.log_beam_cut;
+    a.q_shift = l.q_shift; a.q_scale = l.q_scale;
+    constexpr int NT = (NS / 4 < 32 ? 32 : NS / 4) + 64;
+    kern<<<l.N, NT, bytes, stream>>>(a);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t of_launch_fwd_beam(const OfFusedLaunch &l, cudaStream_t stream) {
+    switch (l.state_len) {
+        case 3: return launch<64, 8>(l, stream);
+        case 4: return launch<256, 8>(l, stream);
+        case 5: return launch<1024, 6>(l, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+size_t of_fwd_beam_max_T(int state_len) {
+    // largest T whose tail arrays fit in 227 KB next to the fixed part of the block's shared memory
+    (void)state_len;
+    return 16384;
+}

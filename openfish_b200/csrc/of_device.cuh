@@ -1,0 +1,103 @@
+// of_device.cuh -- sm_100a device primitives shared by the decode kernels: mbarrier-tracked
+// bulk asynchronous copies (global -> shared, no cluster multicast), bounded waits, warp
+// reductions.
+#pragma once
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace ofd {
+
+// Status codes a kernel can raise in the gpubuf's status word (0 = fine).
+enum : int {
+    kStatusOk = 0,
+    kStatusWaitTimeout = 1,  // a bulk copy never signalled its barrier within the time limit
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t arrivals) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(arrivals)
+                 : "memory");
+}
+// Make barrier initialisation visible to the asynchronous proxy before the first bulk copy.
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Wait for phase `parity` of `bar`, but never for longer than about two seconds and never once
+// the block's abort flag is up.  On timeout the abort flag and the global status word are set
+// and the caller carries on (with meaningless data) so that every barrier in the kernel is
+// still reached and the kernel ends; the host then reports the status instead of results.
+__device__ __forceinline__ void mbar_wait_bounded(uint64_t *bar, uint32_t parity,
+                                                  volatile int *abort_flag, int *status) {
+    if (mbar_try_wait(bar, parity)) return;
+    uint64_t t0 = 0;
+    for (uint32_t spin = 1;; ++spin) {
+        if (*abort_flag) return;
+        if (mbar_try_wait(bar, parity)) return;
+        if ((spin & 63u) == 0) {
+            __nanosleep(64);
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > 2000000000ull) {
+                *abort_flag = 1;
+                atomicExch(status, kStatusWaitTimeout);
+                return;
+            }
+        }
+    }
+}
+
+// 1-D bulk asynchronous copy global -> this CTA's shared memory, completion counted in bytes
+// on `bar`.  dst, src and bytes must be multiples of 16.  No multicast.
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes,
+                                         uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// Order-preserving map float -> int32 (and back) so integer warp reductions can take a max.
+__device__ __forceinline__ int float_order_key(float f) {
+    const int i = __float_as_int(f);
+    return i ^ ((i >> 31) & 0x7fffffff);
+}
+__device__ __forceinline__ float float_from_order_key(int k) {
+    return __int_as_float(k ^ ((k >> 31) & 0x7fffffff));
+}
+__device__ __forceinline__ float warp_max(float v) {
+    return float_from_order_key(__reduce_max_sync(0xffffffffu, float_order_key(v)));
+}
+
+}  // namespace ofd
