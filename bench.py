@@ -1,0 +1,305 @@
+#!/usr/bin/env python
+"""Benchmark of the CRF-CTC decode hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one decode of one batch of synthetic scores: hac model, state_len 4, T = 1666,
+N = 512 chunks per GPU, C = 1024, fp16 (the single-GPU configuration the headline metric is
+quoted on).  With N GPUs every rank decodes its own 512 chunks (chunks are independent, so the
+batch is sharded by chunk index with no data-path collective; weak scaling).
+
+`value` is decoded chunks per second with the scores already resident in HBM, timed on the
+device with the CUDA events the library records on the stream its kernels run on; `e2e` is the
+same metric through openfish_decode_gpu with the scores starting in (page-locked) host memory
+and the results ending in host memory.  `roofline` describes the kernel that takes the most
+device time; `cpu_baseline` is the reference CPU decoder on this box's host cores on a bounded
+sample.  One JSON line is printed by rank 0.
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+STATE_LEN, T, N_PER_GPU = 4, 1666, 512
+NS = 4 ** STATE_LEN
+C = 4 * NS
+SEED = 0x0F16
+METRIC = "decoded chunks/sec (hac, T=1666)"
+UNIT = "chunks/s"
+WORKLOAD = ("hac CRF decode: state_len=4 (256 states), T=1666, N=%d chunks per GPU, C=1024 fp16 "
+            "[T][N][C], 5*tanh(1.5z)+4 planted path, DECODER_INIT options" % N_PER_GPU)
+
+CONFIG = {"workload": WORKLOAD,
+          "l2": "inputs (1.75 GB scores + 0.87 GB bwd per GPU) exceed the 126 MB L2; no flush needed",
+          "sharding": "by chunk index, one rank per GPU, no collective"}
+
+# algorithmic bytes per chunk (fp16 scores read once per scan; bwd written then read; post,
+# moves, sequence, qstring written)
+B_BWD = T * 4 * NS * 2 + (T + 1) * NS * 4
+B_FUSED = T * 4 * NS * 2 + 2 * (T + 1) * NS * 4 + 3 * T
+B_CHUNK = 2 * T * 4 * NS * 2 + 3 * (T + 1) * NS * 4 + 3 * T
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+        except Exception:
+            pass
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+def ncu_traffic(kernel):
+    """DRAM bytes per launch of `kernel` from the committed ncu summary, if there is one."""
+    p = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(p):
+        try:
+            return json.load(open(p)).get(kernel)
+        except Exception:
+            return None
+    return None
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while a region runs."""
+
+    def __init__(self, index, period=0.02):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period
+        self.samples, self.reasons, self.sm_max = [], set(), None
+        self._stop_evt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.sm_max = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {"hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+                 "hw_power_brake": getattr(nv, "nvmlClocksEventReasonHwPowerBrakeSlowdown", 0x80)}
+        get = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        while not self._stop_evt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = get(self.h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def finish(self):
+        self._stop_evt.set()
+        if self.is_alive():
+            self.join(timeout=2)
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.sm_max,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def physical_gpu_index(local_rank):
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except Exception:
+            return local_rank
+    return local_rank
+
+
+def cpu_decode_rate(scores32, threads, repeats=1):
+    """chunks/s of the reference CPU decoder (the compiled reference when present, else the
+    restatement) on a float32 [T][n][C] sample."""
+    import oracle
+    kind = "reference" if oracle.have_ref() else "port"
+    fn = oracle.ref_decode if kind == "reference" else oracle.decode
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        fn(scores32, STATE_LEN, None, threads)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return scores32.shape[1] / best, kind, best
+
+
+def host_sample(n_chunks, seed):
+    import numpy as np
+    from openfish_b200 import synth
+    return synth.make_scores(T, n_chunks, STATE_LEN, seed).astype(np.float32)
+
+
+def run_reference(args, rank, world):
+    """The reference arm: the reference's own CPU implementation of the path on the host cores."""
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    n = max(cores, min(N_PER_GPU, 2 * cores))  # a bounded sample of the workload per step
+    n = min(n, N_PER_GPU)
+    sc = host_sample(n, SEED)
+    for _ in range(max(0, min(args.warmup, 1))):
+        cpu_decode_rate(sc, cores)
+    times, kind = [], "port"
+    for _ in range(args.steps):
+        rate, kind, dt = cpu_decode_rate(sc, cores)
+        times.append(dt)
+    total = sum(times)
+    value = n * len(times) / total
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32 storage, f64 exp/log (the CPU decoder's arithmetic)", "data": "synthetic",
+            "config": CONFIG, "sample_chunks_per_step": n,
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": min(cores, n), "kind": kind,
+                             "sample": "%d chunks of the workload per step, openfish_decode_cpu with %d threads" % (n, min(cores, n))},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import openfish_b200 as of
+    from openfish_b200 import sharding, synth
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    # this rank's shard: chunks [rank*512, (rank+1)*512) of the job, generated in its own HBM
+    lo, hi = sharding.shard_range(N_PER_GPU * world, rank, world)
+    n_local = hi - lo
+    scores = synth.make_scores_device(T, n_local, STATE_LEN, SEED + rank, dev)
+    gb = of.gpubuf_init(T, n_local, STATE_LEN)
+    res = [torch.empty((n_local, T), dtype=torch.uint8).pin_memory() for _ in range(3)]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident throughput (value) -------------------------------------------
+    for _ in range(args.warmup):
+        of.decode_into(scores, STATE_LEN, gb, *res)
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    barrier()
+    sampler.start()
+    ms = {"bwd_scan": 0.0, "fwd_beam": 0.0, "d2h": 0.0, "total": 0.0}
+    w0 = time.perf_counter()
+    for _ in range(args.steps):
+        of.decode_into(scores, STATE_LEN, gb, *res)
+        for k, v in gb.last_decode_ms().items():
+            ms[k] += v
+    barrier()
+    wall = time.perf_counter() - w0
+    bases_local = float(res[0].sum())
+    dev_s = sharding.max_over_ranks(ms["total"] * 1e-3, dev if world > 1 else None)
+    wall_s = sharding.max_over_ranks(wall, dev if world > 1 else None)
+    total_chunks = N_PER_GPU * world
+    value = total_chunks * args.steps / dev_s
+    bases = sharding.sum_over_ranks(bases_local, dev if world > 1 else None)
+
+    # ---- end to end through the reference-facing call, host buffers -----------------------
+    h_scores = torch.empty(scores.shape, dtype=torch.float16).pin_memory()
+    h_scores.copy_(scores)
+    d_in = torch.empty_like(scores)
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        d_in.copy_(h_scores, non_blocking=True)
+        of.decode_gpu(d_in, STATE_LEN, gpubuf=gb)
+    barrier()
+    e0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        d_in.copy_(h_scores, non_blocking=True)   # H2D on the legacy default stream
+        out = of.decode_gpu(d_in, STATE_LEN, gpubuf=gb)  # openfish_decode_gpu: results malloc'ed on the host
+        _ = int(out["moves"][0, 0])
+    barrier()
+    e2e_s = sharding.max_over_ranks(time.perf_counter() - e0, dev if world > 1 else None)
+    clocks = sampler.finish()
+    e2e_value = total_chunks * e2e_steps / e2e_s
+
+    if rank == 0:
+        peak, peak_src = measured_peak()
+        per = {k: v / args.steps for k, v in ms.items()}
+        dom = "bwd_scan" if per["bwd_scan"] >= per["fwd_beam"] else "fwd_beam"
+        dom_bytes = (B_BWD if dom == "bwd_scan" else B_FUSED) * n_local
+        achieved = dom_bytes / (per[dom] * 1e-3) / 1e9
+        whole = B_CHUNK * n_local / (per["total"] * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1e3 * dev_s / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32 storage, f64 inside the log-sum-exp, fp16 scores", "data": "synthetic",
+            "config": CONFIG, "chunks_total": total_chunks,
+            "timing": "CUDA events recorded by the library on its own stream, summed over steps, max over ranks",
+            "bases_per_sec": bases / dev_s * 1.0,
+            "wall_ms_per_step": 1e3 * wall_s / args.steps,
+            "kernel_ms": {"bwd_scan": per["bwd_scan"], "fwd_beam": per["fwd_beam"], "d2h": per["d2h"]},
+            "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": ncu_traffic(dom), "peak_source": peak_src,
+                         "algorithmic_bytes_per_launch": dom_bytes},
+            "roofline_whole_decode": {"achieved": whole, "peak": peak, "unit": "GB/s", "frac": whole / peak,
+                                      "algorithmic_bytes_per_chunk": B_CHUNK},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(scores.numel() * 2),
+                    "d2h_bytes_per_step": int(3 * n_local * T), "steps": e2e_steps,
+                    "call": "openfish_decode_gpu after a page-locked host-to-device copy of the scores"},
+            "gpu_launches": of.lib().openfish_b200_kernels_per_decode() * args.steps,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            cores = os.cpu_count() or 1
+            n_s = min(N_PER_GPU, max(cores, 128))
+            sc32 = scores[:, :n_s, :].float().cpu().numpy()
+            rate, kind, dt = cpu_decode_rate(np.ascontiguousarray(sc32), cores)
+            line["cpu_baseline"] = {"value": rate, "unit": UNIT, "cores": min(cores, n_s), "kind": kind,
+                                    "sample": "first %d chunks of the same batch, one openfish_decode_cpu call, %.2f s" % (n_s, dt)}
+        print(json.dumps(line), flush=True)
+    gb.free()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -202,9 +202,4 @@ def rotary_emb_gpu(x_gpu, sin_gpu, cos_gpu, batch_size, seqlen, nheads, head_dim
     _check()
 
 
-def shard_range(n_chunks, rank, world):
-    """Contiguous chunk range [lo, hi) of `rank` when `n_chunks` chunks are split over `world`
-    GPUs by chunk index (earlier ranks take the remainder)."""
-    each, extra = divmod(n_chunks, world)
-    lo = rank * each + min(rank, extra)
-    return lo, lo + each + (1 if rank < extra else 0)
+from .sharding import shard_range  # noqa: E402,F401

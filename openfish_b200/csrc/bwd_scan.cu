@@ -116,14 +116,15 @@ bwd_scan_kernel(const __half *__restrict__ scores, float *__restrict__ bwd, int 
         const float nxt[4] = {nx.x, nx.y, nx.z, nx.w};
 
         float res[4] = {0.f, 0.f, 0.f, 0.f};
+        if (live) {  // a padding chunk of the last block has no data to work on
+            float v[4][5];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            if (!live) break;  // a padding chunk of the last block has no data to work on
-            float v[5];
-            v[0] = own[k] + stay;
+            for (int k = 0; k < 4; ++k) {
+                v[k][0] = own[k] + stay;
 #pragma unroll
-            for (int b = 0; b < 4; ++b) v[b + 1] = nxt[b] + half_at(lo, hi, 4 * b + k);
-            res[k] = ofx::lse5_exact(v, tr);
+                for (int b = 0; b < 4; ++b) v[k][b + 1] = nxt[b] + half_at(lo, hi, 4 * b + k);
+            }
+            ofx::lse5_batch_exact<4>(v, res, tr);
         }
         float *arow = sm.alpha[(i & 1) ^ 1][cl];
         float *grow = out_chunk + (size_t)t * NS;

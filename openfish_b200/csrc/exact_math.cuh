@@ -192,6 +192,67 @@ OFX_HD float lse5_exact(const float v[5], const TabRef t) {
     return (float)r;
 }
 
+// K independent five-term log-sum-exps at once, same arithmetic as lse5_exact.  The work is
+// written stage by stage across all 5K exponentials so that the FP64 pipe always has
+// independent operations in flight (one lse5_exact after another leaves it waiting on its own
+// dependency chain most of the time).
+template <int K>
+OFX_HD void lse5_batch_exact(const float (*v)[5], float *out, const TabRef t) {
+    const double kMagic = 6755399441055744.0;
+    const double kInvStep = 46.16624130844682903551758979206;
+    const double kStep = 0.021660849392498290194649070354;
+    float m[K];
+    double x[K * 5], r[K * 5], p[K * 5];
+    int n[K * 5];
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+        m[k] = v[k][0];
+#pragma unroll
+        for (int i = 1; i < 5; ++i) m[k] = m[k] > v[k][i] ? m[k] : v[k][i];
+#pragma unroll
+        for (int i = 0; i < 5; ++i) {
+            float a = m[k] - v[k][i];
+            a = a < 80.0f ? a : 80.0f;
+            x[k * 5 + i] = widen_nonneg(a);
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < K * 5; ++q) p[q] = d_fma(x[q], -kInvStep, kMagic);
+#pragma unroll
+    for (int q = 0; q < K * 5; ++q) {
+        n[q] = (int)lo_word(p[q]);
+        r[q] = d_add(p[q], -kMagic);
+    }
+#pragma unroll
+    for (int q = 0; q < K * 5; ++q) r[q] = d_fma(r[q], -kStep, -x[q]);
+#pragma unroll
+    for (int q = 0; q < K * 5; ++q) p[q] = d_fma(r[q], 1.0 / 120.0, 1.0 / 24.0);
+#pragma unroll
+    for (int q = 0; q < K * 5; ++q) p[q] = d_fma(p[q], r[q], 1.0 / 6.0);
+#pragma unroll
+    for (int q = 0; q < K * 5; ++q) p[q] = d_fma(p[q], r[q], 0.5);
+#pragma unroll
+    for (int q = 0; q < K * 5; ++q) p[q] = d_fma(p[q], r[q], 1.0);
+#pragma unroll
+    for (int q = 0; q < K * 5; ++q) p[q] = d_fma(p[q], r[q], 1.0);
+#pragma unroll
+    for (int q = 0; q < K * 5; ++q) {
+        const double e = d_mul(t.exp2_j[(n[q] & 31) * t.exp_stride], p[q]);
+        p[q] = make_double(hi_word(e) + (uint32_t)((n[q] >> 5) << 20), lo_word(e));
+    }
+    double s[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) s[k] = round_to_f32(p[k * 5]);
+#pragma unroll
+    for (int i = 1; i < 5; ++i) {
+#pragma unroll
+        for (int k = 0; k < K; ++k) s[k] = round_to_f32(d_add(s[k], p[k * 5 + i]));
+    }
+#pragma unroll
+    for (int k = 0; k < K; ++k)
+        out[k] = (float)d_add(widen(m[k]), log_1to8(s[k], t.rcp_c, t.log_c));
+}
+
 // The reference's two-term fold used when beam elements merge (src/beam_search.c:43-47):
 //   d = |x - y| (float);  m = max;  return (float)(m + (d < 17 ? log(1.0 + exp(-(double)d)) : 0))
 OFX_HD float fold2_exact(float x, float y, const TabRef t) {

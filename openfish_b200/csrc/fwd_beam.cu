@@ -9,7 +9,9 @@
 //
 // Roles inside a block (one chunk):
 //   scan warps   ns/4 threads, four consecutive states each: forward recursion in shared memory
-//                (one named barrier per timestep) and the posterior softmax of fwd+bwd.  The
+//                (one named barrier per timestep), in the same value-exact arithmetic as the
+//                backward scan so that fwd+bwd equals the CPU's float for float, and the
+//                posterior softmax of fwd+bwd.  The
 //                softmax needs no per-row maximum: the log partition function is the same for
 //                every row, so one offset taken from row 0 keeps every exponent in range; the
 //                row sum is reduced across warps and applied one timestep late.
@@ -42,23 +44,7 @@ __device__ __forceinline__ float ex2_approx(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-__device__ __forceinline__ float lg2_approx(float x) {
-    float y;
-    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr float kLn2 = 0.6931471805599453f;
-
-// Five-term log-sum-exp in fast fp32 (the forward scores only feed the posterior, which is
-// compared within a tolerance, not bit for bit).
-__device__ __forceinline__ float lse5_fast(float a, float b, float c, float d, float e) {
-    const float m = fmaxf(fmaxf(fmaxf(a, b), fmaxf(c, d)), e);
-    const float s = ex2_approx((a - m) * kLog2e) + ex2_approx((b - m) * kLog2e) +
-                    ex2_approx((c - m) * kLog2e) + ex2_approx((d - m) * kLog2e) +
-                    ex2_approx((e - m) * kLog2e);
-    return fmaf(lg2_approx(s), kLn2, m);
-}
 
 __device__ __forceinline__ float half_bits_to_float(uint32_t w, int odd) {
     return __half2float(__ushort_as_half((unsigned short)(odd ? (w >> 16) : (w & 0xffffu))));
@@ -100,6 +86,7 @@ struct FusedSmem {
     uint32_t bloom[128];
     int init_state[kBeam];
     double exp2_j[ofx::kExpTab];
+    alignas(16) double exp2_rep[ofx::kExpTab * 16];  // per-lane copies for the scan warps
     double rcp_c[ofx::kLogTab];
     double log_c[ofx::kLogTab];
     alignas(8) uint64_t full[RING];
@@ -154,6 +141,7 @@ fwd_beam_kernel(const FusedArgs a) {
         own_beam_ring ? reinterpret_cast<unsigned char *>(&sm) + sizeof(Smem) : &sm.score_ring[0][0];
 
     for (int i = tid; i < ofx::kExpTab; i += NT) sm.exp2_j[i] = a.tables->exp2_j[i];
+    for (int i = tid; i < ofx::kExpTab * 16; i += NT) sm.exp2_rep[i] = a.tables->exp2_j[i / 16];
     for (int i = tid; i < ofx::kLogTab; i += NT) {
         sm.rcp_c[i] = a.tables->rcp_c[i];
         sm.log_c[i] = a.tables->log_c[i];
@@ -205,6 +193,7 @@ fwd_beam_kernel(const FusedArgs a) {
         const int j = tid;
         const bool act = j < TPC;
         const int sw = (j >> 2) & 1;
+        const ofx::TabRef scan_tr = {sm.exp2_rep + (lane & 15), 16, sm.rcp_c, sm.log_c};
         if (act) *reinterpret_cast<float4 *>(&sm.alpha[0][4 * j]) = make_float4(0.f, 0.f, 0.f, 0.f);
         // softmax offset: maximum of fwd+bwd at row 0 (= bwd row 0, fwd is zero there)
         ofd::mbar_wait_bounded(&sm.full[0], 0, &sm.abort_flag, a.status);
@@ -243,15 +232,18 @@ fwd_beam_kernel(const FusedArgs a) {
                 const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
                 const float ow[4] = {own.x, own.y, own.z, own.w};
                 const float bv[4] = {bw.x, bw.y, bw.z, bw.w};
+                float v[4][5];
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     // state 4j+k: predecessors j + b*ns/4, score columns 4(4j+k) + b
-                    nw[k] = lse5_fast(ow[k] + a.stay, p0 + half_bits_to_float(w[2 * k], 0),
-                                      p1 + half_bits_to_float(w[2 * k], 1),
-                                      p2 + half_bits_to_float(w[2 * k + 1], 0),
-                                      p3 + half_bits_to_float(w[2 * k + 1], 1));
+                    v[k][0] = ow[k] + a.stay;
+                    v[k][1] = p0 + half_bits_to_float(w[2 * k], 0);
+                    v[k][2] = p1 + half_bits_to_float(w[2 * k], 1);
+                    v[k][3] = p2 + half_bits_to_float(w[2 * k + 1], 0);
+                    v[k][4] = p3 + half_bits_to_float(w[2 * k + 1], 1);
                     e[k] = ex2_approx(((ow[k] + bv[k]) - m0) * kLog2e);
                 }
+                ofx::lse5_batch_exact<4>(v, nw, scan_tr);
                 *reinterpret_cast<float4 *>(&sm.alpha[(t & 1) ^ 1][4 * j]) =
                     make_float4(nw[0], nw[1], nw[2], nw[3]);
             }

@@ -60,6 +60,10 @@ def _oracle():
         lib.oracle_rotary_emb.restype = None
         lib.oracle_rotary_emb.argtypes = [_fp, _fp, _fp, C.c_int, C.c_int, C.c_int, C.c_int,
                                           C.c_long, C.c_long, C.c_long]
+        lib.oracle_fold_scores.restype = C.c_float
+        lib.oracle_fold_scores.argtypes = [C.c_float, C.c_float]
+        lib.oracle_backward_scan.restype = None
+        lib.oracle_backward_scan.argtypes = [_fp, _fp, C.c_int, C.c_int, C.c_int, C.c_int]
         lib.oracle_crc32c.restype = C.c_uint32
         lib.oracle_crc32c.argtypes = [C.c_uint32, C.c_uint32, C.c_int]
         _libs["o"] = lib
@@ -95,6 +99,22 @@ def _ref():
 
 def crc32c(crc, bits, nbits):
     return int(_oracle().oracle_crc32c(crc, bits, nbits))
+
+
+def fold_scores(x, y):
+    """The reference's two-term log-sum-exp used when beam elements merge."""
+    return float(_oracle().oracle_fold_scores(x, y))
+
+
+def backward_scan(scores, state_len):
+    """bwd [N][T+1][ns] from the restatement's backward scan alone."""
+    scores = np.ascontiguousarray(scores, dtype=np.float32)
+    T, N, _ = scores.shape
+    ns = 4 ** state_len
+    out = np.zeros((N, T + 1, ns), np.float32)
+    for c in range(N):
+        _oracle().oracle_backward_scan(scores, out, c, T, N, ns)
+    return out
 
 
 def decode(scores, state_len, opt=None, nthreads=1, tensors=False):

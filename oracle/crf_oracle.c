@@ -155,6 +155,9 @@ static float fold_scores(float x, float y) {
     return m + ((d < 17.0f) ? log(1.0 + exp(-d)) : 0.0f);
 }
 
+/* exported for the arithmetic checks of the CUDA path's two-term fold */
+float oracle_fold_scores(float x, float y) { return fold_scores(x, y); }
+
 static int cmp_desc(const void *a, const void *b) {
     const float x = *(const float *)a, y = *(const float *)b;
     return (x < y) - (x > y);

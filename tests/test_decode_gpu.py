@@ -1,0 +1,179 @@
+"""Parity of the CUDA decode path, called through the C ABI, with the CPU oracle.
+
+Gates (stated in gpu_util.compare / assert_parity): backward scores bit-identical; posterior
+within 1e-3 absolutely and within 1e-3 relatively where it is at least 0.01; moves and sequence
+byte-identical on at least 99.9 % of chunks (mismatching chunks are listed with their edit
+distance in the failure message); qstring within +-1 Phred on sequence-identical chunks."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from conftest import SYNTH_CASES, load_golden
+from gpu_util import assert_parity, compare, gpu_decode, sequences
+
+pytestmark = pytest.mark.gpu
+
+
+def check(of, oracle, sc16, sl, okw=None, threads=16, **gates):
+    okw = okw or {}
+    ref = oracle.decode(sc16.astype(np.float32), sl, oracle.decoder_init(**okw), nthreads=threads, tensors=True)
+    out = gpu_decode(of, sc16, sl, of.decoder_init(**okw))
+    rep = compare(out, ref)
+    assert_parity(rep, **gates)
+    return out, ref, rep
+
+
+def test_reference_golden_vector(native_lib, oracle_mod):
+    g = load_golden("ref_fast_chunk")
+    out = gpu_decode(native_lib, g["scores"], 3, native_lib.decoder_init(q_scale=0.97, q_shift=-1.8), tensors=False)
+    assert np.array_equal(out["moves"], g["moves"]) and np.array_equal(out["sequence"], g["sequence"])
+    assert np.abs(out["qstring"].astype(int) - g["qstring"].astype(int)).max() <= 1
+
+
+@pytest.mark.parametrize("name", SYNTH_CASES)
+def test_fixtures_from_reference(native_lib, name):
+    g = load_golden("synth_" + name)
+    out = gpu_decode(native_lib, g["scores"], g["state_len"], native_lib.decoder_init(**g["options"]))
+    rep = compare(out, g)
+    assert_parity(rep, min_identical=1.0)
+
+
+def test_config_fast_T1000_N16(native_lib, oracle_mod):
+    from openfish_b200 import synth
+    check(native_lib, oracle_mod, synth.make_scores(1000, 16, 3, 0x0F15), 3, min_identical=1.0)
+
+
+def test_hac_T1666(native_lib, oracle_mod):
+    from openfish_b200 import synth
+    check(native_lib, oracle_mod, synth.make_scores(1666, 48, 4, 0x0F16), 4, min_identical=1.0)
+
+
+def test_sup_T1666(native_lib, oracle_mod):
+    from openfish_b200 import synth
+    check(native_lib, oracle_mod, synth.make_scores(1666, 6, 5, 0x0F17), 5, min_identical=1.0)
+
+
+@pytest.mark.parametrize("sl,T,N", [(3, 1, 1), (3, 2, 3), (3, 7, 5), (4, 9, 1), (3, 257, 7), (4, 513, 3),
+                                    (5, 3, 2), (3, 300, 9)])
+def test_ragged_shapes(native_lib, oracle_mod, sl, T, N):
+    from openfish_b200 import synth
+    check(native_lib, oracle_mod, synth.make_scores(T, N, sl, 40 + T + N), sl, min_identical=1.0)
+
+
+@pytest.mark.parametrize("sl,C", [(3, 320), (4, 1280), (3, 264)])
+def test_wide_rows_keep_the_reference_two_stride_addressing(native_lib, oracle_mod, sl, C):
+    # C > 4*ns: scans stride by N*4ns, beam search by N*C, exactly like the CPU decoder
+    from openfish_b200 import synth
+    check(native_lib, oracle_mod, synth.make_scores(120, 5, sl, 60 + C, C=C), sl, min_identical=1.0)
+
+
+@pytest.mark.parametrize("p_step", [0.15, 0.5])
+def test_stay_heavy_paths_merge_duplicates(native_lib, oracle_mod, p_step):
+    from openfish_b200 import synth
+    check(native_lib, oracle_mod, synth.make_scores(600, 12, 3, 71, p_step=p_step), 3, min_identical=1.0)
+    check(native_lib, oracle_mod, synth.make_scores(400, 6, 4, 72, p_step=p_step), 4, min_identical=1.0)
+
+
+def test_degenerate_scores(native_lib, oracle_mod):
+    # all candidates tie (bisection guess limit, 32-way clamp), and golden-like mostly -5 scores
+    z = np.zeros((50, 3, 256), np.float16)
+    check(native_lib, oracle_mod, z, 3, min_identical=1.0)
+    rng = np.random.default_rng(5)
+    s = np.full((400, 4, 256), -5.0, np.float16)
+    s[rng.random(s.shape) < 0.3] = 2.0
+    check(native_lib, oracle_mod, s, 3, min_identical=1.0)
+
+
+@pytest.mark.parametrize("okw", [dict(beam_cut=0.0), dict(beam_cut=1.5), dict(beam_cut=1e6),
+                                 dict(q_scale=0.95, q_shift=-0.2), dict(q_scale=3.0, q_shift=10.0)])
+def test_options(native_lib, oracle_mod, okw):
+    from openfish_b200 import synth
+    check(native_lib, oracle_mod, synth.make_scores(300, 6, 4, 81, p_step=0.7), 4, okw, min_identical=1.0)
+
+
+def test_into_and_submit_wait_match_decode_gpu(native_lib):
+    import torch
+    from openfish_b200 import synth
+    of = native_lib
+    sc = torch.from_numpy(synth.make_scores(200, 10, 3, 91)).cuda()
+    gb = of.gpubuf_init(200, 10, 3)
+    base = of.decode_gpu(sc, 3, gpubuf=gb)
+    pinned = [torch.zeros((10, 200), dtype=torch.uint8).pin_memory() for _ in range(3)]
+    of.decode_into(sc, 3, gb, *pinned)
+    pageable = [torch.zeros((10, 200), dtype=torch.uint8) for _ in range(3)]
+    of.decode_into(sc, 3, gb, *pageable, wait=False)
+    of.decode_wait(gb)
+    for k, a, b in zip(("moves", "sequence", "qstring"), pinned, pageable):
+        assert np.array_equal(a.numpy(), base[k]) and np.array_equal(b.numpy(), base[k])
+    ms = gb.last_decode_ms()
+    assert ms["bwd_scan"] > 0 and ms["fwd_beam"] > 0 and ms["total"] >= ms["bwd_scan"] + ms["fwd_beam"] - 1e-3
+    gb.free()
+
+
+def test_argument_errors(native_lib):
+    import torch
+    of = native_lib
+    lib = of.lib()
+    lib.set_openfish_log_level(0)
+    try:
+        sc = torch.zeros((20, 4, 256), dtype=torch.float16, device="cuda")
+        gb = of.gpubuf_init(20, 4, 3)
+        with pytest.raises(of.OpenfishError) as e:
+            of.decode_gpu(torch.zeros((21, 4, 256), dtype=torch.float16, device="cuda"), 3, gpubuf=gb)
+        assert e.value.status == 3  # shape differs from the gpubuf's
+        with pytest.raises(of.OpenfishError) as e:
+            of.decode_gpu(sc, 3, options=of.decoder_init(beam_width=16), gpubuf=gb)
+        assert e.value.status == 4
+        small = of.gpubuf_init(20, 4, 4)
+        with pytest.raises(of.OpenfishError) as e:
+            of.decode_gpu(sc, 4, gpubuf=small)  # C=256 < 4*256
+        assert e.value.status == 2
+        small.free()
+        # misaligned scores pointer
+        flat = torch.zeros(20 * 4 * 256 + 8, dtype=torch.float16, device="cuda")
+        out = [C.c_void_p() for _ in range(3)]
+        opt = of.decoder_init()
+        lib.openfish_decode_gpu(20, 4, 256, flat.data_ptr() + 2, 3, C.byref(opt), gb.ptr, *[C.byref(o) for o in out])
+        assert lib.openfish_b200_last_status() == 2 and out[0].value is None
+        # a good call still works afterwards
+        assert of.decode_gpu(sc, 3, gpubuf=gb)["moves"].shape == (4, 20)
+        gb.free()
+    finally:
+        lib.set_openfish_log_level(4)
+
+
+def test_full_size_hac_properties_and_sampled_parity(native_lib, oracle_mod):
+    """BASELINE-sized batch (hac, T=1666, N=512): size-independent properties on all chunks and
+    oracle parity on a sample of them."""
+    import torch
+    from openfish_b200 import synth
+    of = native_lib
+    T, N, sl = 1666, 512, 4
+    d = synth.make_scores_device(T, N, sl, 0x0F16, "cuda")
+    gb = of.gpubuf_init(T, N, sl)
+    a = of.decode_gpu(d, sl, gpubuf=gb)
+    bwd_last = gb.tensor("bwd_NTC")[:, T, :]
+    assert float(bwd_last.abs().max()) == 0.0
+    rows = gb.tensor("post_NTC")[::37].sum(-1)
+    assert float((rows - 1).abs().max()) < 1e-4
+    b = of.decode_gpu(d, sl, gpubuf=gb)  # same input, same buffers: identical output
+    for k in a:
+        assert np.array_equal(a[k], b[k])
+    lens = a["moves"].sum(1)
+    assert (a["moves"][:, 0] == 1).all()
+    for n in range(0, N, 17):
+        s, q = a["sequence"][n], a["qstring"][n]
+        assert set(bytes(s[: lens[n]])) <= set(b"ACGT") and not s[lens[n]:].any() and not q[lens[n]:].any()
+        assert q[: lens[n]].min() >= 34 and q[: lens[n]].max() <= 83
+    # a chunk's result does not depend on its batch: decode a subset alone
+    idx = np.arange(3, N, 41)
+    sub = d[:, torch.from_numpy(idx).cuda(), :].contiguous()
+    alone = of.decode_gpu(sub, sl)
+    for k in a:
+        assert np.array_equal(alone[k], a[k][idx])
+    # oracle on the sampled chunks
+    ref = oracle_mod.decode(sub.cpu().numpy().astype(np.float32), sl, nthreads=16)
+    rep = compare(alone, ref)
+    assert_parity(rep, min_identical=1.0)
+    gb.free()

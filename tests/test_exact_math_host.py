@@ -1,0 +1,77 @@
+"""The double-precision exp/log kernels of the CUDA backward scan, built for the host, against
+libm and against the CPU oracle's backward scan (bit for bit)."""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+@pytest.fixture(scope="module")
+def host():
+    src = os.path.join(HERE, "host_model", "exact_math_host.cpp")
+    so = os.path.join(HERE, "host_model", "libexact_math_host.so")
+    subprocess.run(["g++", "-O2", "-fPIC", "-shared", "-ffp-contract=off", "-o", so, src], check=True)
+    lib = C.CDLL(so)
+    fp = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
+    lib.host_backward_scan.argtypes = [fp, fp, C.c_int, C.c_int, C.c_int, C.c_int]
+    lib.host_fold2.restype = C.c_float
+    lib.host_fold2.argtypes = [C.c_float, C.c_float]
+    for f in ("host_exp_neg", "host_log_1to8", "host_round_to_f32"):
+        getattr(lib, f).restype = C.c_double
+        getattr(lib, f).argtypes = [C.c_double]
+    return lib
+
+
+def test_exp_log_accuracy(host):
+    rng = np.random.default_rng(0)
+    a = np.concatenate([rng.uniform(0, 20, 5000), rng.uniform(0, 80, 1000), [0.0, 17.0, 80.0]])
+    err = max(abs(host.host_exp_neg(x) - np.exp(-x)) for x in a)
+    assert err < 2.0 ** -45
+    assert host.host_exp_neg(0.0) == 1.0
+    y = np.concatenate([rng.uniform(1, 8, 6000), [1.0, 2.0, 4.0, 5.0, np.nextafter(8.0, 0)]])
+    err = max(abs(host.host_log_1to8(v) - np.log(v)) for v in y)
+    assert err < 2.0 ** -43
+
+
+def test_round_to_f32_matches_conversion(host):
+    rng = np.random.default_rng(1)
+    v = np.concatenate([rng.uniform(0.5, 8, 4000), np.exp(rng.uniform(-80, 2, 4000)),
+                        # exact ties between neighbouring floats
+                        (np.float32(1.0) + np.arange(1, 200, 2) * 2.0 ** -24).astype(np.float64)])
+    for x in v:
+        assert host.host_round_to_f32(float(x)) == float(np.float32(x))
+
+
+def test_fold_matches_oracle(host, oracle_mod):
+    rng = np.random.default_rng(2)
+    x = rng.uniform(-3000, 3000, 4000).astype(np.float32)
+    y = (x + rng.uniform(-20, 20, 4000)).astype(np.float32)
+    for a, b in zip(x, y):
+        assert host.host_fold2(a, b) == oracle_mod.fold_scores(a, b)
+    big = np.float32(-3.4028234663852886e38)
+    for a, b in ((big, 1.0), (big, big), (5.0, 5.0), (0.0, 17.0), (0.0, 16.999)):
+        assert host.host_fold2(a, b) == oracle_mod.fold_scores(a, b)
+
+
+@pytest.mark.parametrize("sl,T,N,seed,p_step", [(3, 800, 6, 11, 1.0), (4, 500, 3, 12, 0.5), (5, 120, 1, 13, 1.0)])
+def test_backward_scan_bit_exact(host, oracle_mod, sl, T, N, seed, p_step):
+    from openfish_b200 import synth
+    sc = synth.make_scores(T, N, sl, seed, p_step=p_step).astype(np.float32)
+    ref = oracle_mod.backward_scan(sc, sl)
+    out = np.zeros_like(ref)
+    for c in range(N):
+        host.host_backward_scan(sc, out, c, T, N, 4 ** sl)
+    assert np.array_equal(out, ref)
+
+
+def test_backward_scan_bit_exact_on_reference_golden(host, oracle_mod):
+    from conftest import load_golden
+    sc = load_golden("ref_fast_chunk")["scores"].astype(np.float32)
+    ref = oracle_mod.backward_scan(sc, 3)
+    out = np.zeros_like(ref)
+    host.host_backward_scan(sc, out, 0, 1666, 1, 64)
+    assert np.array_equal(out, ref)

@@ -1,0 +1,62 @@
+"""Chunk-index sharding across ranks (the multi-GPU path), exercised with gloo on CPU.  The
+CPU oracle stands in for the per-rank decode, which checks what sharding relies on: a chunk's
+result does not depend on which other chunks share its batch."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_shard_range_partitions():
+    from openfish_b200.sharding import shard_range
+    for n in (1, 7, 16, 512, 4096, 4099):
+        for world in (1, 2, 3, 4, 8):
+            spans = [shard_range(n, r, world) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == n
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            sizes = [hi - lo for lo, hi in spans]
+            assert max(sizes) - min(sizes) <= 1 and sizes == sorted(sizes, reverse=True)
+    assert [shard_range(4096, r, 8) for r in (0, 7)] == [(0, 512), (3584, 4096)]
+
+
+def _worker(rank, world, port, n_chunks, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import torch.distributed as dist
+    import oracle
+    from openfish_b200 import sharding, synth
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    sc = synth.make_scores(60, n_chunks, 3, 21)
+    lo, hi = sharding.shard_range(n_chunks, rank, world)
+    mine = sharding.slice_scores(sc, lo, hi).astype(np.float32)
+    out = oracle.decode(mine, 3)
+    seq = sharding.gather_rows(out["sequence"], n_chunks)
+    mv = sharding.gather_rows(out["moves"], n_chunks)
+    slowest = sharding.max_over_ranks(1.0 + rank)
+    total = sharding.sum_over_ranks(hi - lo)
+    if rank == 0:
+        q.put((seq, mv, slowest, total))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,n_chunks", [(2, 5), (2, 8)])
+def test_sharded_decode_equals_whole_batch(oracle_mod, world, n_chunks):
+    import torch.multiprocessing as mp
+    from openfish_b200 import synth
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() % 2000) + n_chunks
+    procs = [ctx.Process(target=_worker, args=(r, world, port, n_chunks, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    seq, mv, slowest, total = q.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    whole = oracle_mod.decode(synth.make_scores(60, n_chunks, 3, 21).astype(np.float32), 3)
+    assert np.array_equal(seq, whole["sequence"]) and np.array_equal(mv, whole["moves"])
+    assert slowest == float(world) and total == float(n_chunks)
