@@ -12,7 +12,7 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libopenfish.so")
+LIB_PATH = os.environ.get("OPENFISH_B200_LIB") or os.path.join(_HERE, "lib", "libopenfish.so")
 
 STATUS_NAMES = ["OK", "ERR_ARGUMENT", "ERR_LAYOUT", "ERR_SHAPE", "ERR_OPTION", "ERR_ALLOC",
                 "ERR_CUDA", "ERR_DEVICE_WAIT", "ERR_NO_CPU_PATH", "ERR_TOO_LONG"]

@@ -7,7 +7,7 @@
 // float after every rounding the CPU performs.  The CPU rounds (a) each running-sum update to
 // float and (b) the final max+log(sum) to float; both roundings are decided correctly as long
 // as exp/log are accurate to far below half a float ulp.  The routines here are accurate to
-// about 2^-46 absolute on their domains (exp on [-80,0], log on [1,8)), which leaves a
+// about 2^-44 absolute on their domains (exp on [-80,0], log on [1,8)), which leaves a
 // mismatch probability per rounding of about 2^-22.
 //
 // The same source compiles for the host (plain C++) so the arithmetic can be checked against
@@ -26,9 +26,9 @@
 
 namespace ofx {
 
-// Tables: 2^(j/32) for the exp; reciprocal and logarithm of interval centres for the log
+// Tables: 2^(j/64) for the exp; reciprocal and logarithm of interval centres for the log
 // (64 intervals per binade over [1,8)).  Filled once on the host by fill_tables().
-constexpr int kExpTab = 32;
+constexpr int kExpTab = 64;
 constexpr int kLogTab = 192;
 struct Tables {
     double exp2_j[kExpTab];
@@ -104,38 +104,25 @@ OFX_HD uint32_t f_bits(float f) {
 #endif
 }
 
-// Exact widening of a non-negative normal float (or +0, which maps to a harmless 2^-126-sized
-// value) with integer operations only, keeping the conversion off the FP64 pipe.
-OFX_HD double widen_nonneg(float a) {
-    const uint32_t b = f_bits(a);
-    return make_double((b >> 3) + 0x38000000u, b << 29);
-}
-// Exact widening of any normal float (sign kept).
-OFX_HD double widen(float a) {
-    const uint32_t b = f_bits(a);
-    return make_double((((b & 0x7fffffffu) >> 3) + 0x38000000u) | (b & 0x80000000u), b << 29);
-}
-
-// exp(-a) for a in [0, 80], a given as a double.  Argument reduction -a = n*ln2/32 + r with
-// |r| <= ln2/64, table 2^(j/32), degree-5 Taylor polynomial.  9 FP64 operations.
-// `tab` holds Tables::exp2_j with entry j at tab[j * stride] (any address space; a kernel may
-// interleave per-lane copies of the table to keep shared-memory reads conflict free).
+// exp(-a) for a in [0, 80], a given as a double.  Argument reduction -a = n*ln2/64 + r with
+// |r| <= ln2/128, table 2^(j/64), degree-4 Taylor polynomial (truncation < 2^-44).  8 FP64
+// operations.  `tab` holds Tables::exp2_j with entry j at tab[j * stride] (any address space; a
+// kernel may interleave per-lane copies of the table to keep shared-memory reads conflict free).
+constexpr double kExpMagic = 6755399441055744.0;  // 1.5 * 2^52: low word of (x + magic) = rint(x)
+constexpr double kExpInvStep = 92.33248261689365807103517958412;   // 64 / ln 2
+constexpr double kExpStep = 0.010830424696249145097324535177;      // ln 2 / 64
 OFX_HD double exp_neg(double a, const double *tab, int stride = 1) {
-    const double kMagic = 6755399441055744.0;  // 1.5 * 2^52: low word of (x + kMagic) = rint(x)
-    const double kInvStep = 46.16624130844682903551758979206;  // 32 / ln 2
-    const double kStep = 0.021660849392498290194649070354;     // ln 2 / 32
-    const double t = d_fma(a, -kInvStep, kMagic);
+    const double t = d_fma(a, -kExpInvStep, kExpMagic);
     const int n = (int)lo_word(t);  // <= 0
-    const double nd = d_add(t, -kMagic);
-    const double r = d_fma(nd, -kStep, -a);
-    double p = d_fma(r, 1.0 / 120.0, 1.0 / 24.0);
-    p = d_fma(p, r, 1.0 / 6.0);
+    const double nd = d_add(t, -kExpMagic);
+    const double r = d_fma(nd, -kExpStep, -a);
+    double p = d_fma(r, 1.0 / 24.0, 1.0 / 6.0);
     p = d_fma(p, r, 0.5);
     p = d_fma(p, r, 1.0);
     p = d_fma(p, r, 1.0);
-    const double e = d_mul(tab[(n & 31) * stride], p);
-    // scale by 2^(n >> 5): results stay far inside the normal range for a <= 80
-    return make_double(hi_word(e) + (uint32_t)((n >> 5) << 20), lo_word(e));
+    const double e = d_mul(tab[(n & 63) * stride], p);
+    // scale by 2^(n >> 6): results stay far inside the normal range for a <= 80
+    return make_double(hi_word(e) + ((uint32_t)(n & ~63) << 14), lo_word(e));
 }
 
 // log(y) for y in [1, 8).  y = c*(1+u) with c the centre of y's 1/64-binade interval;
@@ -185,10 +172,10 @@ OFX_HD float lse5_exact(const float v[5], const TabRef t) {
     for (int i = 0; i < 5; ++i) {
         float a = m - v[i];          // = -(v[i] - m) exactly
         a = a < 80.0f ? a : 80.0f;   // exp(-80) is far below anything a float sum >= 1 can see
-        const double e = exp_neg(widen_nonneg(a), t.exp2_j, t.exp_stride);
+        const double e = exp_neg((double)a, t.exp2_j, t.exp_stride);
         s = i == 0 ? round_to_f32(e) : round_to_f32(d_add(s, e));
     }
-    const double r = d_add(widen(m), log_1to8(s, t.rcp_c, t.log_c));
+    const double r = d_add((double)m, log_1to8(s, t.rcp_c, t.log_c));
     return (float)r;
 }
 
@@ -198,9 +185,6 @@ OFX_HD float lse5_exact(const float v[5], const TabRef t) {
 // dependency chain most of the time).
 template <int K>
 OFX_HD void lse5_batch_exact(const float (*v)[5], float *out, const TabRef t) {
-    const double kMagic = 6755399441055744.0;
-    const double kInvStep = 46.16624130844682903551758979206;
-    const double kStep = 0.021660849392498290194649070354;
     float m[K];
     double x[K * 5], r[K * 5], p[K * 5];
     int n[K * 5];
@@ -213,22 +197,20 @@ OFX_HD void lse5_batch_exact(const float (*v)[5], float *out, const TabRef t) {
         for (int i = 0; i < 5; ++i) {
             float a = m[k] - v[k][i];
             a = a < 80.0f ? a : 80.0f;
-            x[k * 5 + i] = widen_nonneg(a);
+            x[k * 5 + i] = (double)a;  // exact; one conversion instead of three integer operations
         }
     }
 #pragma unroll
-    for (int q = 0; q < K * 5; ++q) p[q] = d_fma(x[q], -kInvStep, kMagic);
+    for (int q = 0; q < K * 5; ++q) p[q] = d_fma(x[q], -kExpInvStep, kExpMagic);
 #pragma unroll
     for (int q = 0; q < K * 5; ++q) {
         n[q] = (int)lo_word(p[q]);
-        r[q] = d_add(p[q], -kMagic);
+        r[q] = d_add(p[q], -kExpMagic);
     }
 #pragma unroll
-    for (int q = 0; q < K * 5; ++q) r[q] = d_fma(r[q], -kStep, -x[q]);
+    for (int q = 0; q < K * 5; ++q) r[q] = d_fma(r[q], -kExpStep, -x[q]);
 #pragma unroll
-    for (int q = 0; q < K * 5; ++q) p[q] = d_fma(r[q], 1.0 / 120.0, 1.0 / 24.0);
-#pragma unroll
-    for (int q = 0; q < K * 5; ++q) p[q] = d_fma(p[q], r[q], 1.0 / 6.0);
+    for (int q = 0; q < K * 5; ++q) p[q] = d_fma(r[q], 1.0 / 24.0, 1.0 / 6.0);
 #pragma unroll
     for (int q = 0; q < K * 5; ++q) p[q] = d_fma(p[q], r[q], 0.5);
 #pragma unroll
@@ -237,8 +219,8 @@ OFX_HD void lse5_batch_exact(const float (*v)[5], float *out, const TabRef t) {
     for (int q = 0; q < K * 5; ++q) p[q] = d_fma(p[q], r[q], 1.0);
 #pragma unroll
     for (int q = 0; q < K * 5; ++q) {
-        const double e = d_mul(t.exp2_j[(n[q] & 31) * t.exp_stride], p[q]);
-        p[q] = make_double(hi_word(e) + (uint32_t)((n[q] >> 5) << 20), lo_word(e));
+        const double e = d_mul(t.exp2_j[(n[q] & 63) * t.exp_stride], p[q]);
+        p[q] = make_double(hi_word(e) + ((uint32_t)(n[q] & ~63) << 14), lo_word(e));
     }
     double s[K];
 #pragma unroll
@@ -250,7 +232,7 @@ OFX_HD void lse5_batch_exact(const float (*v)[5], float *out, const TabRef t) {
     }
 #pragma unroll
     for (int k = 0; k < K; ++k)
-        out[k] = (float)d_add(widen(m[k]), log_1to8(s[k], t.rcp_c, t.log_c));
+        out[k] = (float)d_add((double)m[k], log_1to8(s[k], t.rcp_c, t.log_c));
 }
 
 // The reference's two-term fold used when beam elements merge (src/beam_search.c:43-47):
@@ -259,7 +241,7 @@ OFX_HD float fold2_exact(float x, float y, const TabRef t) {
     const float d = fabsf(x - y);
     const float m = x > y ? x : y;
     if (!(d < 17.0f)) return m;
-    const double e = exp_neg(widen_nonneg(d), t.exp2_j, t.exp_stride);
+    const double e = exp_neg((double)d, t.exp2_j, t.exp_stride);
     const double l = log_1to8(d_add(1.0, e), t.rcp_c, t.log_c);
     return (float)d_add((double)m, l);
 }

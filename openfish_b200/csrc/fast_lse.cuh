@@ -1,0 +1,92 @@
+// fast_lse.cuh -- fp32 evaluation of the reference's five-term log-sum-exp that knows when it
+// is right.
+//
+// The value-exact routine in exact_math.cuh costs about 60 FP64 operations per state and
+// timestep.  Most of the time that effort is not needed to know which float the reference
+// arithmetic produces: the result max + log(sum) is rounded to a float whose spacing grows with
+// the magnitude of the scores (2^-12 once they pass 2048), while log(sum) can be had in fp32
+// to about 2^-20.  So: evaluate log(sum) in fp32, widen it by a bound on every error that
+// separates it from the reference's own value, add both ends of that interval to the maximum
+// with one correctly rounded float addition each, and accept when both ends land on the same
+// float (rounding is monotone, so the reference's result is pinned between them).  Otherwise
+// the caller falls back to the value-exact routine.  Nothing is approximated in what is
+// accepted.
+//
+// Error budget of log(sum), all relative to sum >= 1 (so also absolute in the logarithm):
+//   ex2.approx: 2 ulp                                   2^-22
+//   rounding of (v-m)*log2(e) before ex2, weighted
+//     by the term's size (max a*exp(-a) = 0.37, 4 terms) 2^-23.4
+//   four float additions here                           2^-22
+//   the reference's four float additions (decode_cpu.c:47) 2^-22
+//   lg2.approx on [1,2): 2^-22 absolute in log2         2^-22.5
+//   q + lg2(f), * ln2, the +-eps additions: float roundings  < 2^-21.5 together
+// Sum < 2^-19.9; kLseEps = 2^-19.5 leaves a margin of a third.
+#pragma once
+#include <cuda_runtime.h>
+
+namespace ofd {
+
+constexpr float kLseEps = 1.3487e-6f;  // 2^-19.5
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float lg2_approx(float x) {
+    float y;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// v: the five terms.  On success writes the reference-exact float to `out`.
+__device__ __forceinline__ bool lse5_try_fast(const float v[5], float &out) {
+    const float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
+    const float m = fmaxf(fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3])), v[4]);
+    float s = ex2_approx((v[0] - m) * kLog2e);
+    s += ex2_approx((v[1] - m) * kLog2e);
+    s += ex2_approx((v[2] - m) * kLog2e);
+    s += ex2_approx((v[3] - m) * kLog2e);
+    s += ex2_approx((v[4] - m) * kLog2e);
+    // s in [1, 5]: split off the power of two so lg2 works on [1,2), where its error is absolute
+    const unsigned bits = __float_as_uint(s);
+    const float q = (float)((int)(bits >> 23) - 127);
+    const float f = __uint_as_float((bits & 0x007fffffu) | 0x3f800000u);
+    const float l = (q + lg2_approx(f)) * kLn2;
+    const float lo = m + (l - kLseEps);
+    const float hi = m + (l + kLseEps);
+    out = lo;
+    // NaN or infinite inputs compare unequal or are caught by the finiteness test
+    return lo == hi && fabsf(lo) < 3.0e38f;
+}
+
+}  // namespace ofd
+
+#include "exact_math.cuh"
+
+namespace ofd {
+
+// K log-sum-exps for one thread: fast path first, value-exact fallback for the states whose
+// rounding the fast path cannot certify.  When most of the warp needs the fallback (the first
+// few hundred timesteps, where scores are small and the float grid is fine) the batched
+// routine does all K at once; otherwise the few lanes concerned redo single states.
+template <int K>
+__device__ __forceinline__ void lse5_batch(const float (*v)[5], float *out, const ofx::TabRef t) {
+    bool ok[K];
+    int fails = 0;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+        ok[k] = lse5_try_fast(v[k], out[k]);
+        fails += __popc(__ballot_sync(0xffffffffu, !ok[k]));
+    }
+    if (fails == 0) return;
+    if (fails > 4 * K) {
+        ofx::lse5_batch_exact<K>(v, out, t);
+        return;
+    }
+#pragma unroll
+    for (int k = 0; k < K; ++k)
+        if (!ok[k]) out[k] = ofx::lse5_exact(v[k], t);
+}
+
+}  // namespace ofd

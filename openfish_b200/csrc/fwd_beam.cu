@@ -8,7 +8,7 @@
 // reference's CUDA kernel lacks -- because output parity is defined against the CPU decoder.
 //
 // Roles inside a block (one chunk):
-//   scan warps   ns/4 threads, four consecutive states each: forward recursion in shared memory
+//   scan warps   ns/SPT threads, SPT consecutive states each: forward recursion in shared memory
 //                (one named barrier per timestep), in the same value-exact arithmetic as the
 //                backward scan so that fwd+bwd equals the CPU's float for float, and the
 //                posterior softmax of fwd+bwd.  The
@@ -31,6 +31,7 @@
 #include <float.h>
 
 #include "exact_math.cuh"
+#include "fast_lse.cuh"
 #include "fwd_beam.cuh"
 #include "of_device.cuh"
 
@@ -39,11 +40,7 @@ namespace {
 constexpr int kBeam = 32;
 constexpr int kWin = 256;  // traceback window, timesteps
 
-__device__ __forceinline__ float ex2_approx(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
+using ofd::ex2_approx;
 constexpr float kLog2e = 1.4426950408889634f;
 
 __device__ __forceinline__ float half_bits_to_float(uint32_t w, int odd) {
@@ -74,13 +71,73 @@ __device__ __forceinline__ uint32_t crc32c_bits(uint32_t crc, uint32_t v, int n)
     return crc;
 }
 
+// SPT (1, 2 or 4) consecutive floats through one vector access.
+template <int SPT>
+__device__ __forceinline__ void load_floats(float (&d)[SPT], const float *p) {
+    if constexpr (SPT == 4) {
+        const float4 v = *reinterpret_cast<const float4 *>(p);
+        d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+    } else if constexpr (SPT == 2) {
+        const float2 v = *reinterpret_cast<const float2 *>(p);
+        d[0] = v.x; d[1] = v.y;
+    } else {
+        d[0] = *p;
+    }
+}
+template <int SPT>
+__device__ __forceinline__ void store_floats(float *p, const float (&d)[SPT]) {
+    if constexpr (SPT == 4) *reinterpret_cast<float4 *>(p) = make_float4(d[0], d[1], d[2], d[3]);
+    else if constexpr (SPT == 2) *reinterpret_cast<float2 *>(p) = make_float2(d[0], d[1]);
+    else *p = d[0];
+}
+// The 4*SPT fp16 scores of SPT consecutive states (8*SPT contiguous bytes) widened to fp32.
+// For SPT = 4 the two 16-byte halves are read in an order that depends on the thread so that a
+// quarter-warp never hits a bank twice.
+template <int SPT>
+__device__ __forceinline__ void load_scores(float (&sc)[SPT * 4], const unsigned char *p, int u) {
+    uint32_t w[SPT * 2];
+    if constexpr (SPT == 4) {
+        const int sw = (u >> 2) & 1;
+        const uint4 q0 = *reinterpret_cast<const uint4 *>(p + 16 * sw);
+        const uint4 q1 = *reinterpret_cast<const uint4 *>(p + 16 * (1 - sw));
+        const uint4 lo = sw ? q1 : q0, hi = sw ? q0 : q1;
+        w[0] = lo.x; w[1] = lo.y; w[2] = lo.z; w[3] = lo.w; w[4] = hi.x; w[5] = hi.y; w[6] = hi.z; w[7] = hi.w;
+    } else if constexpr (SPT == 2) {
+        const uint4 q = *reinterpret_cast<const uint4 *>(p);
+        w[0] = q.x; w[1] = q.y; w[2] = q.z; w[3] = q.w;
+    } else {
+        const uint2 q = *reinterpret_cast<const uint2 *>(p);
+        w[0] = q.x; w[1] = q.y;
+    }
+#pragma unroll
+    for (int i = 0; i < SPT * 2; ++i) {
+        sc[2 * i] = half_bits_to_float(w[i], 0);
+        sc[2 * i + 1] = half_bits_to_float(w[i], 1);
+    }
+}
+template <int NW>
+__device__ __forceinline__ float sum_partials(const float *p) {
+    float s = 0.f;
+    if constexpr (NW % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < NW; i += 4) {
+            const float4 v = *reinterpret_cast<const float4 *>(p + i);
+            s += (v.x + v.y) + (v.z + v.w);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < NW; ++i) s += p[i];
+    }
+    return s;
+}
+
 template <int NS, int RING>
 struct FusedSmem {
     static constexpr int kScoreRow = NS * 8;  // bytes of one fp16 score row
     static constexpr int kBwdRow = NS * 4;    // bytes of one fp32 backward row
     alignas(16) float alpha[2][NS];
-    float psum[2][8];
-    float red[8];
+    alignas(16) float psum[2][32];
+    float red[32];
     alignas(16) uint4 rec[kBeam];
     alignas(16) float cstep[kBeam * 4];
     uint32_t bloom[128];
@@ -92,7 +149,7 @@ struct FusedSmem {
     alignas(8) uint64_t full[RING];
     alignas(8) uint64_t empty[RING];
     int abort_flag;
-    int part[352];  // block-scan partials of the tail phase
+    int part[608];  // block-scan partials of the tail phase
     // rings last: the tail phase reuses them (and whatever dynamic shared memory follows)
     alignas(128) unsigned char score_ring[RING][kScoreRow];
     alignas(128) unsigned char bwd_ring[RING][kBwdRow];
@@ -116,13 +173,14 @@ struct FusedArgs {
     float stay, log_beam_cut, q_shift, q_scale;
 };
 
-template <int NS, int RING>
-__global__ void __launch_bounds__((NS / 4 < 32 ? 32 : NS / 4) + 64)
+template <int NS, int SPT, int RING>
+__global__ void __launch_bounds__((NS / SPT < 32 ? 32 : NS / SPT) + 64)
 fwd_beam_kernel(const FusedArgs a) {
     constexpr int BITS = (NS == 64) ? 6 : (NS == 256 ? 8 : 10);
     constexpr int SL = BITS / 2;
     constexpr int MSB = NS / 4;
-    constexpr int TPC = NS / 4;                 // scan threads that own states
+    constexpr int TPC = NS / SPT;               // scan threads that own states (SPT each)
+    static_assert(TPC % 32 == 0, "scan warps must be full: they vote with the full mask");
     constexpr int TPAD = TPC < 32 ? 32 : TPC;   // scan threads including idle lanes
     constexpr int NFW = TPAD / 32;              // scan warps
     constexpr int NT = TPAD + 64;
@@ -190,17 +248,23 @@ fwd_beam_kernel(const FusedArgs a) {
         }
     } else if (warp < NFW) {
         // ------------------------------------------------------------------ scan warps
-        const int j = tid;
-        const bool act = j < TPC;
-        const int sw = (j >> 2) & 1;
+        const int u = tid;
+        const bool act = u < TPC;
+        const int s0 = u * SPT;   // this thread's states s0 .. s0+SPT-1
+        const int pj = s0 >> 2;   // their shared predecessors are pj + b*ns/4
         const ofx::TabRef scan_tr = {sm.exp2_rep + (lane & 15), 16, sm.rcp_c, sm.log_c};
-        if (act) *reinterpret_cast<float4 *>(&sm.alpha[0][4 * j]) = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (act) {
+#pragma unroll
+            for (int k = 0; k < SPT; ++k) sm.alpha[0][s0 + k] = 0.f;
+        }
         // softmax offset: maximum of fwd+bwd at row 0 (= bwd row 0, fwd is zero there)
         ofd::mbar_wait_bounded(&sm.full[0], 0, &sm.abort_flag, a.status);
         float m0 = -FLT_MAX;
         if (act) {
-            const float4 b0 = *reinterpret_cast<const float4 *>(sm.bwd_ring[0] + 16 * j);
-            m0 = fmaxf(fmaxf(b0.x, b0.y), fmaxf(b0.z, b0.w));
+            float b0[SPT];
+            load_floats<SPT>(b0, reinterpret_cast<const float *>(sm.bwd_ring[0]) + s0);
+#pragma unroll
+            for (int k = 0; k < SPT; ++k) m0 = fmaxf(m0, b0[k]);
         }
         m0 = ofd::warp_max(m0);
         if (lane == 0) sm.red[warp] = m0;
@@ -209,68 +273,68 @@ fwd_beam_kernel(const FusedArgs a) {
 #pragma unroll
         for (int w = 1; w < NFW; ++w) m0 = fmaxf(m0, sm.red[w]);
 
-        float e_prev[4] = {0.f, 0.f, 0.f, 0.f};
+        float e_prev[SPT];
+#pragma unroll
+        for (int k = 0; k < SPT; ++k) e_prev[k] = 0.f;
         for (int t = 0; t <= T; ++t) {
             const int slot = t % RING;
-            ofd::mbar_wait_bounded(&sm.full[slot], (uint32_t)(t / RING) & 1u, &sm.abort_flag,
-                                   a.status);
-            float nw[4] = {0.f, 0.f, 0.f, 0.f};
-            float e[4] = {0.f, 0.f, 0.f, 0.f};
+            float nw[SPT], e[SPT];
+#pragma unroll
+            for (int k = 0; k < SPT; ++k) nw[k] = e[k] = 0.f;
             if (act) {
                 const float *ain = sm.alpha[t & 1];
-                const float4 own = *reinterpret_cast<const float4 *>(ain + 4 * j);
-                const float p0 = ain[j], p1 = ain[j + MSB], p2 = ain[j + 2 * MSB], p3 = ain[j + 3 * MSB];
-                const float4 bw = *reinterpret_cast<const float4 *>(sm.bwd_ring[slot] + 16 * j);
-                uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
+                float ow[SPT], bv[SPT], sc[SPT * 4];
+                load_floats<SPT>(ow, ain + s0);
+                const float p0 = ain[pj], p1 = ain[pj + MSB], p2 = ain[pj + 2 * MSB], p3 = ain[pj + 3 * MSB];
+                load_floats<SPT>(bv, reinterpret_cast<const float *>(sm.bwd_ring[slot]) + s0);
                 if (t < T) {
-                    const unsigned char *row = sm.score_ring[slot] + 32 * j;
-                    const uint4 q0 = *reinterpret_cast<const uint4 *>(row + 16 * sw);
-                    const uint4 q1 = *reinterpret_cast<const uint4 *>(row + 16 * (1 - sw));
-                    lo = sw ? q1 : q0;
-                    hi = sw ? q0 : q1;
-                }
-                const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-                const float ow[4] = {own.x, own.y, own.z, own.w};
-                const float bv[4] = {bw.x, bw.y, bw.z, bw.w};
-                float v[4][5];
+                    load_scores<SPT>(sc, sm.score_ring[slot] + 8 * s0, u);
+                } else {
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    // state 4j+k: predecessors j + b*ns/4, score columns 4(4j+k) + b
+                    for (int i = 0; i < SPT * 4; ++i) sc[i] = 0.f;  // src/decode_cpu.c:99
+                }
+                float v[SPT][5];
+#pragma unroll
+                for (int k = 0; k < SPT; ++k) {
+                    // state s0+k: score columns 4(s0+k) + b
                     v[k][0] = ow[k] + a.stay;
-                    v[k][1] = p0 + half_bits_to_float(w[2 * k], 0);
-                    v[k][2] = p1 + half_bits_to_float(w[2 * k], 1);
-                    v[k][3] = p2 + half_bits_to_float(w[2 * k + 1], 0);
-                    v[k][4] = p3 + half_bits_to_float(w[2 * k + 1], 1);
+                    v[k][1] = p0 + sc[4 * k];
+                    v[k][2] = p1 + sc[4 * k + 1];
+                    v[k][3] = p2 + sc[4 * k + 2];
+                    v[k][4] = p3 + sc[4 * k + 3];
                     e[k] = ex2_approx(((ow[k] + bv[k]) - m0) * kLog2e);
                 }
-                ofx::lse5_batch_exact<4>(v, nw, scan_tr);
-                *reinterpret_cast<float4 *>(&sm.alpha[(t & 1) ^ 1][4 * j]) =
-                    make_float4(nw[0], nw[1], nw[2], nw[3]);
+                ofd::lse5_batch<SPT>(v, nw, scan_tr);
+                store_floats<SPT>(&sm.alpha[(t & 1) ^ 1][s0], nw);
             }
-            float part = (e[0] + e[1]) + (e[2] + e[3]);
+            float part = 0.f;
+#pragma unroll
+            for (int k = 0; k < SPT; ++k) part += e[k];
 #pragma unroll
             for (int o = 16; o; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
             if (lane == 0) sm.psum[t & 1][warp] = part;
             if (t > 0 && act) {
-                float s = sm.psum[(t - 1) & 1][0];
+                const float inv = 1.0f / sum_partials<NFW>(sm.psum[(t - 1) & 1]);
+                float o[SPT];
 #pragma unroll
-                for (int w = 1; w < NFW; ++w) s += sm.psum[(t - 1) & 1][w];
-                const float inv = 1.0f / s;
-                *reinterpret_cast<float4 *>(post_chunk + (size_t)(t - 1) * NS + 4 * j) =
-                    make_float4(e_prev[0] * inv, e_prev[1] * inv, e_prev[2] * inv, e_prev[3] * inv);
+                for (int k = 0; k < SPT; ++k) o[k] = e_prev[k] * inv;
+                store_floats<SPT>(post_chunk + (size_t)(t - 1) * NS + s0, o);
             }
 #pragma unroll
-            for (int k = 0; k < 4; ++k) e_prev[k] = e[k];
+            for (int k = 0; k < SPT; ++k) e_prev[k] = e[k];
+            // one thread checks that the next row has landed; the barrier passes that on
+            if (tid == 0 && t < T)
+                ofd::mbar_wait_bounded(&sm.full[(t + 1) % RING], (uint32_t)((t + 1) / RING) & 1u,
+                                       &sm.abort_flag, a.status);
             ofd::named_bar_sync(1, TPAD);
             if (tid == 0) ofd::mbar_arrive(&sm.empty[slot]);
         }
         if (act) {
-            float s = sm.psum[T & 1][0];
+            const float inv = 1.0f / sum_partials<NFW>(sm.psum[T & 1]);
+            float o[SPT];
 #pragma unroll
-            for (int w = 1; w < NFW; ++w) s += sm.psum[T & 1][w];
-            const float inv = 1.0f / s;
-            *reinterpret_cast<float4 *>(post_chunk + (size_t)T * NS + 4 * j) =
-                make_float4(e_prev[0] * inv, e_prev[1] * inv, e_prev[2] * inv, e_prev[3] * inv);
+            for (int k = 0; k < SPT; ++k) o[k] = e_prev[k] * inv;
+            store_floats<SPT>(post_chunk + (size_t)T * NS + s0, o);
         }
     } else {
         // ------------------------------------------------------------------ beam warp
@@ -619,7 +683,7 @@ fwd_beam_kernel(const FusedArgs a) {
 
 namespace {
 
-template <int NS, int RING>
+template <int NS, int SPT, int RING>
 cudaError_t launch(const OfFusedLaunch &l, cudaStream_t stream) {
     using Smem = FusedSmem<NS, RING>;
     const int Tp = (l.T + 16) & ~15;
@@ -629,7 +693,7 @@ cudaError_t launch(const OfFusedLaunch &l, cudaStream_t stream) {
     size_t bytes = sizeof(Smem) + extra + 128;
     if (tail > ring_bytes + extra) bytes += tail - (ring_bytes + extra);
     if (bytes > 227 * 1024) return cudaErrorInvalidValue;
-    auto kern = fwd_beam_kernel<NS, RING>;
+    auto kern = fwd_beam_kernel<NS, SPT, RING>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
     if (e != cudaSuccess) return e;
     FusedArgs a;
@@ -639,7 +703,7 @@ cudaError_t launch(const OfFusedLaunch &l, cudaStream_t stream) {
     a.total_probs = l.total_probs; a.tables = l.tables; a.status = l.status;
     a.T = l.T; a.N = l.N; a.C = l.C; a.stay = l.stay; a.log_beam_cut = l.log_beam_cut;
     a.q_shift = l.q_shift; a.q_scale = l.q_scale;
-    constexpr int NT = (NS / 4 < 32 ? 32 : NS / 4) + 64;
+    constexpr int NT = (NS / SPT < 32 ? 32 : NS / SPT) + 64;
     kern<<<l.N, NT, bytes, stream>>>(a);
     return cudaGetLastError();
 }
@@ -648,9 +712,9 @@ cudaError_t launch(const OfFusedLaunch &l, cudaStream_t stream) {
 
 cudaError_t of_launch_fwd_beam(const OfFusedLaunch &l, cudaStream_t stream) {
     switch (l.state_len) {
-        case 3: return launch<64, 8>(l, stream);
-        case 4: return launch<256, 8>(l, stream);
-        case 5: return launch<1024, 6>(l, stream);
+        case 3: return launch<64, 1, 8>(l, stream);
+        case 4: return launch<256, 2, 8>(l, stream);
+        case 5: return launch<1024, 2, 6>(l, stream);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -169,11 +169,12 @@ def test_full_size_hac_properties_and_sampled_parity(native_lib, oracle_mod):
     # a chunk's result does not depend on its batch: decode a subset alone
     idx = np.arange(3, N, 41)
     sub = d[:, torch.from_numpy(idx).cuda(), :].contiguous()
-    alone = of.decode_gpu(sub, sl)
+    gb.free()
+    sub16 = sub.cpu().numpy()
+    alone = gpu_decode(of, sub16, sl)
     for k in a:
         assert np.array_equal(alone[k], a[k][idx])
-    # oracle on the sampled chunks
-    ref = oracle_mod.decode(sub.cpu().numpy().astype(np.float32), sl, nthreads=16)
+    # oracle on the sampled chunks, tensors included (backward scores must be bit-identical)
+    ref = oracle_mod.decode(sub16.astype(np.float32), sl, nthreads=16, tensors=True)
     rep = compare(alone, ref)
     assert_parity(rep, min_identical=1.0)
-    gb.free()
