@@ -29,7 +29,8 @@ enum openfish_b200_status {
     OPENFISH_B200_ERR_CUDA = 6,        /* a CUDA call failed; see openfish_b200_error_text */
     OPENFISH_B200_ERR_DEVICE_WAIT = 7, /* a kernel gave up waiting for an asynchronous copy */
     OPENFISH_B200_ERR_NO_CPU_PATH = 8, /* openfish_decode_cpu / openfish_rotary_emb_cpu called */
-    OPENFISH_B200_ERR_TOO_LONG = 9     /* T beyond what one block's shared memory can trace back */
+    OPENFISH_B200_ERR_TOO_LONG = 9,    /* T beyond what one block's shared memory can trace back */
+    OPENFISH_B200_ERR_SCRATCH_LIMIT = 10 /* shape needs more than the static scratch array holds */
 };
 
 /* 0 (default): behave like the reference -- print the error and exit(EXIT_FAILURE).
@@ -65,6 +66,36 @@ void openfish_b200_last_decode_ms(const openfish_gpubuf_t *gpubuf, float ms[4]);
 
 /* Number of kernels one decode call launches (for benchmark bookkeeping). */
 int openfish_b200_kernels_per_decode(void);
+
+/* Decode without allocating anything, for callers that cannot let a library allocate once they
+ * are running: a serving process that has handed all free device memory to its own arena (a
+ * later cudaMalloc from here would fail or fragment it), or a steady-state pipeline that must
+ * not run into the device-wide synchronisation cudaMalloc / cudaFree imply.  This entry point has
+ * no counterpart in the reference.
+ *
+ * Same decode, same options and same requirements on scores_TNC as openfish_decode_gpu, but no
+ * gpubuf: every intermediate lives in one fixed device array of
+ * OPENFISH_B200_STATIC_SCRATCH_BYTES that the library carries (each GPU on which the library's
+ * code gets loaded holds it until the process exits).  moves_gpu, sequence_gpu and qstring_gpu
+ * are DEVICE buffers of N*T bytes each, owned by the caller.  The work runs on the legacy default
+ * stream; the call returns when it is done.  It calls no cudaMalloc, cudaFree, cudaMallocHost,
+ * malloc or other allocating routine.
+ *
+ *   - Shapes whose intermediates do not fit are refused with OPENFISH_B200_ERR_SCRATCH_LIMIT:
+ *     needed = 2*N*(T+1)*4^state_len*4 + N*(T+1)*32 + N*T*28 bytes (+ 5 KB), e.g. fast T=1666 up
+ *     to N=52, hac up to N=14, sup up to N=3.
+ *   - All calls on one GPU share the array.  It keeps what the previous call left (the call
+ *     clears what has to start from zero itself); two calls that overlap on the same GPU race,
+ *     so serialise them.
+ *   - The first call on each device resolves the array's device address and uploads 4 KB of
+ *     tables: make that call before any stream capture begins.
+ *
+ * Returns an openfish_b200_status value (0 = OK); errors are also printed subject to the log
+ * level.  It never terminates the process and does not touch openfish_b200_last_status(). */
+#define OPENFISH_B200_STATIC_SCRATCH_BYTES (48u << 20)
+int openfish_b200_decode_static(int T, int N, int C, const void *scores_TNC, int state_len,
+                                const openfish_opt_t *options, uint8_t *moves_gpu,
+                                char *sequence_gpu, char *qstring_gpu);
 
 #ifdef __cplusplus
 }

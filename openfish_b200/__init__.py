@@ -15,7 +15,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("OPENFISH_B200_LIB") or os.path.join(_HERE, "lib", "libopenfish.so")
 
 STATUS_NAMES = ["OK", "ERR_ARGUMENT", "ERR_LAYOUT", "ERR_SHAPE", "ERR_OPTION", "ERR_ALLOC",
-                "ERR_CUDA", "ERR_DEVICE_WAIT", "ERR_NO_CPU_PATH", "ERR_TOO_LONG"]
+                "ERR_CUDA", "ERR_DEVICE_WAIT", "ERR_NO_CPU_PATH", "ERR_TOO_LONG", "ERR_SCRATCH_LIMIT"]
+STATIC_SCRATCH_BYTES = 48 << 20
 
 
 class OpenfishError(RuntimeError):
@@ -84,6 +85,8 @@ def lib():
         L.openfish_b200_error_text.restype = C.c_char_p
         L.openfish_b200_set_error_mode.argtypes = [i]
         L.openfish_b200_kernels_per_decode.restype = i
+        L.openfish_b200_decode_static.restype = i
+        L.openfish_b200_decode_static.argtypes = [i, i, i, vp, i, C.POINTER(Opt), vp, vp, vp]
         L.get_openfish_log_level.restype = i
         L.set_openfish_log_level.argtypes = [i]
         # Python callers get exceptions instead of the reference's exit(1)
@@ -186,6 +189,18 @@ def decode_into(scores_TNC, state_len, gpubuf, moves, sequence, qstring, options
     fn = lib().openfish_b200_decode_into if wait else lib().openfish_b200_decode_submit
     fn(*args, moves.data_ptr(), sequence.data_ptr(), qstring.data_ptr())
     _check()
+
+
+def decode_static(scores_TNC, state_len, moves_gpu, sequence_gpu, qstring_gpu, options=None):
+    """openfish_b200_decode_static: the decode that allocates nothing.  Results go to three
+    caller-owned CUDA uint8 tensors [N][T]; intermediates live in the library's fixed device
+    array, so the shape must fit OPENFISH_B200_STATIC_SCRATCH_BYTES.  Returns the status code
+    (0 = OK) instead of raising, like the C entry point."""
+    T, N, Cc = scores_TNC.shape
+    return lib().openfish_b200_decode_static(T, N, Cc, scores_TNC.data_ptr(), state_len,
+                                             C.byref(options or decoder_init()),
+                                             moves_gpu.data_ptr(), sequence_gpu.data_ptr(),
+                                             qstring_gpu.data_ptr())
 
 
 def decode_wait(gpubuf):
