@@ -187,7 +187,7 @@ cudaError_t of_launch_bwd_scan(const void *scores_fp16, float *bwd, int T, int N
     const __half *s = static_cast<const __half *>(scores_fp16);
     switch (state_len) {
         case 3: return launch<64, 1, 2, 8>(s, bwd, T, N, stay, tables, status, stream);
-        case 4: return launch<256, 2, 1, 8>(s, bwd, T, N, stay, tables, status, stream);
+        case 4: return launch<256, 4, 1, 8>(s, bwd, T, N, stay, tables, status, stream);
         case 5: return launch<1024, 2, 1, 6>(s, bwd, T, N, stay, tables, status, stream);
         default: return cudaErrorInvalidValue;
     }

@@ -73,20 +73,73 @@ namespace ofd {
 template <int K>
 __device__ __forceinline__ void lse5_batch(const float (*v)[5], float *out, const ofx::TabRef t) {
     bool ok[K];
-    int fails = 0;
+    // all K fast evaluations stage by stage, so that their instruction streams interleave
+    {
+        const float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
+        float m[K], e[K][5], s[K], l[K];
 #pragma unroll
-    for (int k = 0; k < K; ++k) {
-        ok[k] = lse5_try_fast(v[k], out[k]);
-        fails += __popc(__ballot_sync(0xffffffffu, !ok[k]));
+        for (int k = 0; k < K; ++k)
+            m[k] = fmaxf(fmaxf(fmaxf(v[k][0], v[k][1]), fmaxf(v[k][2], v[k][3])), v[k][4]);
+#pragma unroll
+        for (int i = 0; i < 5; ++i)
+#pragma unroll
+            for (int k = 0; k < K; ++k) e[k][i] = (v[k][i] - m[k]) * kLog2e;
+#pragma unroll
+        for (int i = 0; i < 5; ++i)
+#pragma unroll
+            for (int k = 0; k < K; ++k) e[k][i] = ex2_approx(e[k][i]);
+#pragma unroll
+        for (int k = 0; k < K; ++k) s[k] = e[k][0] + e[k][1];
+#pragma unroll
+        for (int i = 2; i < 5; ++i)
+#pragma unroll
+            for (int k = 0; k < K; ++k) s[k] += e[k][i];
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+            const unsigned bits = __float_as_uint(s[k]);
+            const float q = (float)((int)(bits >> 23) - 127);
+            const float f = __uint_as_float((bits & 0x007fffffu) | 0x3f800000u);
+            l[k] = (q + lg2_approx(f)) * kLn2;
+        }
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+            const float lo = m[k] + (l[k] - kLseEps);
+            const float hi = m[k] + (l[k] + kLseEps);
+            out[k] = lo;
+            ok[k] = lo == hi && fabsf(lo) < 3.0e38f;
+        }
     }
+    int nbad = 0;
+#pragma unroll
+    for (int k = 0; k < K; ++k) nbad += !ok[k];
+    const int fails = __reduce_add_sync(0xffffffffu, nbad);
     if (fails == 0) return;
     if (fails > 4 * K) {
         ofx::lse5_batch_exact<K>(v, out, t);
         return;
     }
+    // A few lanes need the exact routine for one of their states: every lane that has one
+    // hands in its first uncertified state, so one pass through the routine serves them all.
+    for (;;) {
+        int pick = -1;
 #pragma unroll
-    for (int k = 0; k < K; ++k)
-        if (!ok[k]) out[k] = ofx::lse5_exact(v[k], t);
+        for (int k = K - 1; k >= 0; --k) pick = ok[k] ? pick : k;
+        if (!__any_sync(0xffffffffu, pick >= 0)) break;
+        float w[5];
+#pragma unroll
+        for (int i = 0; i < 5; ++i) {
+            w[i] = v[0][i];
+#pragma unroll
+            for (int k = 1; k < K; ++k) w[i] = pick == k ? v[k][i] : w[i];
+        }
+        const float r = ofx::lse5_exact(w, t);
+#pragma unroll
+        for (int k = 0; k < K; ++k)
+            if (pick == k) {
+                out[k] = r;
+                ok[k] = true;
+            }
+    }
 }
 
 }  // namespace ofd

@@ -43,6 +43,29 @@ constexpr int kWin = 256;  // traceback window, timesteps
 using ofd::ex2_approx;
 constexpr float kLog2e = 1.4426950408889634f;
 
+// Warp maximum of a float through the sm_100a float reduction instruction.
+__device__ __forceinline__ float warp_max_f32(float v) {
+    float r;
+    asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+    return r;
+}
+
+// The reference's two-term fold (src/beam_search.c:43-47): certified fp32 evaluation first (same
+// interval argument as fast_lse.cuh: log1p(exp(-d)) in fp32 is within 2^-20.5 of the reference's
+// double value; if both ends of that interval round to the same float next to m, that float is
+// the reference's), value-exact routine otherwise.
+__device__ __forceinline__ float fold2(float x, float y, const ofx::TabRef t) {
+    const float d = fabsf(x - y);
+    const float m = x > y ? x : y;
+    if (!(d < 17.0f)) return m;
+    const float e = ofd::ex2_approx(-d * 1.4426950408889634f);
+    const float l = ofd::lg2_approx(1.0f + e) * 0.6931471805599453f;
+    const float eps = 6.75e-7f;  // 2^-20.5
+    const float lo = m + (l - eps), hi = m + (l + eps);
+    if (lo == hi && fabsf(lo) < 3.0e38f) return lo;
+    return ofx::fold2_exact(x, y, t);
+}
+
 __device__ __forceinline__ float half_bits_to_float(uint32_t w, int odd) {
     return __half2float(__ushort_as_half((unsigned short)(odd ? (w >> 16) : (w & 0xffffu))));
 }
@@ -140,7 +163,8 @@ struct FusedSmem {
     float red[32];
     alignas(16) uint4 rec[kBeam];
     alignas(16) float cstep[kBeam * 4];
-    uint32_t bloom[128];
+    alignas(8) uint2 slot[2 * kBeam];  // compaction (+ one spare per lane): {score, parent slot | stay << 5 | base << 6}
+    unsigned char owner[8192 + 32];    // (+ one spare per lane) hash -> slot + 1 of the beam element owning it (duplicate detection)
     int init_state[kBeam];
     double exp2_j[ofx::kExpTab];
     alignas(16) double exp2_rep[ofx::kExpTab * 16];  // per-lane copies for the scan warps
@@ -204,7 +228,8 @@ fwd_beam_kernel(const FusedArgs a) {
         sm.rcp_c[i] = a.tables->rcp_c[i];
         sm.log_c[i] = a.tables->log_c[i];
     }
-    for (int i = tid; i < 128; i += NT) sm.bloom[i] = 0;
+    for (int i = tid; i < 2048 + 8; i += NT) reinterpret_cast<uint32_t *>(sm.owner)[i] = 0;
+    for (int i = tid; i < kBeam * 4; i += NT) sm.cstep[i] = __int_as_float(0x7fc00000);  // mailbox: NaN = empty
     if (tid == 0) {
         sm.abort_flag = 0;
         for (int r = 0; r < RING; ++r) {
@@ -378,7 +403,7 @@ fwd_beam_kernel(const FusedArgs a) {
 
         for (int t = 0; t < T; ++t) {
             const int slot_a = t % RING, slot_b = (t + 1) % RING;
-            ofd::mbar_wait_bounded(&sm.full[slot_a], (uint32_t)(t / RING) & 1u, &sm.abort_flag, a.status);
+            // row t was confirmed when it served as "next row" one step ago (or before the loop)
             ofd::mbar_wait_bounded(&sm.full[slot_b], (uint32_t)((t + 1) / RING) & 1u, &sm.abort_flag, a.status);
             const __half *srow = reinterpret_cast<const __half *>(beam_ring + (size_t)slot_a * Smem::kScoreRow);
             const float *brow = reinterpret_cast<const float *>(sm.bwd_ring[slot_b]);
@@ -387,34 +412,55 @@ fwd_beam_kernel(const FusedArgs a) {
             const int top = state >> (BITS - 2);
             const uint32_t b_own = (uint32_t)state & 3u;
 
+            // duplicate-prefix detection (src/beam_search.c:281-316): a stay can only merge with a
+            // step whose parent's hash is `need`.  Every element writes its slot number into an
+            // 8192-entry owner table indexed by its hash; a stay then finds the one candidate
+            // parent by a single look-up and confirms it by comparing the full hash.  If two
+            // elements landed on the same table entry the table cannot be trusted for this
+            // timestep and the exhaustive comparison below takes over.
+            const uint32_t need = crc_unstep2(hash, b_own);
+            // idle slots (lane >= W) use a private spare entry so that nothing here branches
+            const uint32_t own_at = act ? (hash & 8191u) : 8192u + lane;
+            sm.owner[own_at] = (unsigned char)(lane + 1);
+            __syncwarp();
+
             // candidates: 4 steps (state' = 4q + b, column 16q + 4b + top) and the stay
             float c0, c1, c2, c3, c4;
-            if (act) {
+            {
+                // idle slots still hold a valid (stale) k-mer: they read like everybody else and
+                // their candidates are voided afterwards
                 const float4 bw = *reinterpret_cast<const float4 *>(brow + 4 * q);
                 const __half *sp = srow + 16 * q + top;
-                c0 = __fadd_rn(__fadd_rn(score, __half2float(sp[0])), bw.x);
-                c1 = __fadd_rn(__fadd_rn(score, __half2float(sp[4])), bw.y);
-                c2 = __fadd_rn(__fadd_rn(score, __half2float(sp[8])), bw.z);
-                c3 = __fadd_rn(__fadd_rn(score, __half2float(sp[12])), bw.w);
-                c4 = __fadd_rn(__fadd_rn(score, a.stay), brow[state]);
-            } else {
-                c0 = c1 = c2 = c3 = c4 = -INFINITY;
+                const float x0 = __half2float(sp[0]), x1 = __half2float(sp[4]);
+                const float x2 = __half2float(sp[8]), x3 = __half2float(sp[12]);
+                const float bs = brow[state];
+                c0 = __fadd_rn(__fadd_rn(score, x0), bw.x);
+                c1 = __fadd_rn(__fadd_rn(score, x1), bw.y);
+                c2 = __fadd_rn(__fadd_rn(score, x2), bw.z);
+                c3 = __fadd_rn(__fadd_rn(score, x3), bw.w);
+                c4 = __fadd_rn(__fadd_rn(score, a.stay), bs);
+                c0 = act ? c0 : -INFINITY;
+                c1 = act ? c1 : -INFINITY;
+                c2 = act ? c2 : -INFINITY;
+                c3 = act ? c3 : -INFINITY;
+                c4 = act ? c4 : -INFINITY;
             }
+            const int mine_back = sm.owner[own_at];
+            const int cand_raw = sm.owner[need & 8191u];
+            const int cand = act ? cand_raw : 0;
+            const uint32_t clash = __ballot_sync(0xffffffffu, mine_back != lane + 1);
+            const uint32_t cand_hash = __shfl_sync(0xffffffffu, hash, (cand - 1) & 31);
+            int mate = (cand > 0 && cand_hash == need) ? cand - 1 : -1;
+            __syncwarp();
+            sm.owner[own_at] = 0;
 
-            // duplicate-prefix merges (src/beam_search.c:281-316)
-            const uint32_t need = crc_unstep2(hash, b_own);
-            if (act) atomicOr(&sm.bloom[(hash >> 5) & 127u], 1u << (hash & 31u));
-            __syncwarp();
-            const bool hit = act && ((sm.bloom[(need >> 5) & 127u] >> (need & 31u)) & 1u);
-            const uint32_t pot = __ballot_sync(0xffffffffu, hit);
-            __syncwarp();
-            if (act) sm.bloom[(hash >> 5) & 127u] = 0u;
-            if (pot) {
-                int mate = -1;
-                bool conflict = false;
+            bool conflict = false;
+            if (clash) {
+                // exhaustive: for every stay that the table points anywhere, compare against
+                // all elements (the reference's semantics, all-pairs)
+                mate = -1;
                 unsigned long long claimed01 = 0ull, claimed23 = 0ull;
-                for (uint32_t rem = pot; rem; rem &= rem - 1) {
-                    const int i = __ffs(rem) - 1;
+                for (int i = 0; i < W; ++i) {
                     const uint32_t need_i = __shfl_sync(0xffffffffu, need, i);
                     const uint32_t b_i = __shfl_sync(0xffffffffu, b_own, i);
                     const uint32_t m = __ballot_sync(0xffffffffu, act && hash == need_i);
@@ -428,57 +474,69 @@ fwd_beam_kernel(const FusedArgs a) {
                         if (lane == i) mate = jj;
                     }
                 }
-                if (__any_sync(0xffffffffu, mate >= 0)) {
-                    *reinterpret_cast<float4 *>(&sm.cstep[4 * lane]) = make_float4(c0, c1, c2, c3);
-                    if (conflict) sm.rec[lane] = make_uint4(hash, b_own, __float_as_uint(c4), 0u);
+            }
+            if (__any_sync(0xffffffffu, mate >= 0)) {
+                if (!conflict) {
+                    // every stay has at most one partner and no step has two: the folds are
+                    // independent.  The stay fetches its partner's step score by shuffle, folds,
+                    // and posts the partner's new score in a mailbox the partner reads.
+                    const int src = mate >= 0 ? mate : lane;
+                    const float y0 = __shfl_sync(0xffffffffu, c0, src), y1 = __shfl_sync(0xffffffffu, c1, src);
+                    const float y2 = __shfl_sync(0xffffffffu, c2, src), y3 = __shfl_sync(0xffffffffu, c3, src);
+                    if (mate >= 0) {
+                        const float x = c4;
+                        const float y = b_own == 0 ? y0 : (b_own == 1 ? y1 : (b_own == 2 ? y2 : y3));
+                        const float f = fold2(x, y, tr);
+                        const bool stay_wins = x > y;
+                        c4 = stay_wins ? f : -FLT_MAX;
+                        sm.cstep[4 * mate + b_own] = stay_wins ? -FLT_MAX : f;
+                    }
                     __syncwarp();
-                    if (!conflict) {
-                        // every stay has at most one partner and no step has two: the folds
-                        // are independent, so all of them run at once
-                        if (mate >= 0) {
-                            const float x = c4, y = sm.cstep[4 * mate + b_own];
-                            const float f = ofx::fold2_exact(x, y, tr);
-                            if (x > y) {
-                                c4 = f;
-                                sm.cstep[4 * mate + b_own] = -FLT_MAX;
-                            } else {
-                                sm.cstep[4 * mate + b_own] = f;
-                                c4 = -FLT_MAX;
-                            }
-                        }
-                        __syncwarp();
-                    } else {
-                        // repeated hashes inside the beam (CRC collisions): replay the
-                        // reference's nested loop, stay-major then slot-minor, on one lane
-                        if (lane == 0) {
-                            for (int i = 0; i < W; ++i) {
-                                const uint32_t h_i = sm.rec[i].x, b_i = sm.rec[i].y;
-                                for (int jj = 0; jj < W; ++jj) {
-                                    if (h_i != crc_step2(sm.rec[jj].x, b_i)) continue;
-                                    const float x = __uint_as_float(sm.rec[i].z);
-                                    const float y = sm.cstep[4 * jj + b_i];
-                                    const float f = ofx::fold2_exact(x, y, tr);
-                                    if (x > y) {
-                                        sm.rec[i].z = __float_as_uint(f);
-                                        sm.cstep[4 * jj + b_i] = -FLT_MAX;
-                                    } else {
-                                        sm.cstep[4 * jj + b_i] = f;
-                                        sm.rec[i].z = __float_as_uint(-FLT_MAX);
-                                    }
+                    const float4 r = *reinterpret_cast<const float4 *>(&sm.cstep[4 * lane]);
+                    c0 = isnan(r.x) ? c0 : r.x;
+                    c1 = isnan(r.y) ? c1 : r.y;
+                    c2 = isnan(r.z) ? c2 : r.z;
+                    c3 = isnan(r.w) ? c3 : r.w;
+                    __syncwarp();
+                    if (mate >= 0) sm.cstep[4 * mate + b_own] = __int_as_float(0x7fc00000);
+                } else {
+                    // repeated hashes inside the beam (CRC collisions): replay the reference's
+                    // nested loop, stay-major then slot-minor, on one lane
+                    *reinterpret_cast<float4 *>(&sm.cstep[4 * lane]) = make_float4(c0, c1, c2, c3);
+                    sm.rec[lane] = make_uint4(hash, b_own, __float_as_uint(c4), 0u);
+                    __syncwarp();
+                    if (lane == 0) {
+                        for (int i = 0; i < W; ++i) {
+                            const uint32_t h_i = sm.rec[i].x, b_i = sm.rec[i].y;
+                            for (int jj = 0; jj < W; ++jj) {
+                                if (h_i != crc_step2(sm.rec[jj].x, b_i)) continue;
+                                const float x = __uint_as_float(sm.rec[i].z);
+                                const float y = sm.cstep[4 * jj + b_i];
+                                const float f = ofx::fold2_exact(x, y, tr);
+                                if (x > y) {
+                                    sm.rec[i].z = __float_as_uint(f);
+                                    sm.cstep[4 * jj + b_i] = -FLT_MAX;
+                                } else {
+                                    sm.cstep[4 * jj + b_i] = f;
+                                    sm.rec[i].z = __float_as_uint(-FLT_MAX);
                                 }
                             }
                         }
-                        __syncwarp();
-                        if (act) c4 = __uint_as_float(sm.rec[lane].z);
                     }
+                    __syncwarp();
+                    if (act) c4 = __uint_as_float(sm.rec[lane].z);
                     const float4 r = *reinterpret_cast<const float4 *>(&sm.cstep[4 * lane]);
                     c0 = r.x; c1 = r.y; c2 = r.z; c3 = r.w;
+                    __syncwarp();
+                    *reinterpret_cast<float4 *>(&sm.cstep[4 * lane]) =
+                        make_float4(__int_as_float(0x7fc00000), __int_as_float(0x7fc00000),
+                                    __int_as_float(0x7fc00000), __int_as_float(0x7fc00000));
                 }
             }
 
-            // pruning threshold (src/beam_search.c:320-381)
-            const float lmax = fmaxf(fmaxf(fmaxf(c0, c1), fmaxf(c2, c3)), c4);
-            const float best = ofd::warp_max(lmax);
+            // pruning threshold (src/beam_search.c:320-381): best - ln(beam_cut); if more than 32
+            // candidates pass, bisect towards 25..32 survivors for at most 9 further guesses
+            const float best = warp_max_f32(fmaxf(fmaxf(fmaxf(c0, c1), fmaxf(c2, c3)), c4));
             float cut = __fsub_rn(best, a.log_beam_cut);
             auto count_at_least = [&](float th) {
                 const int n = (c0 >= th) + (c1 >= th) + (c2 >= th) + (c3 >= th) + (c4 >= th);
@@ -505,36 +563,47 @@ fwd_beam_kernel(const FusedArgs a) {
                 }
                 kept = min(kept, kBeam);
             }
+            const uint32_t B0 = __ballot_sync(0xffffffffu, c0 >= cut), B1 = __ballot_sync(0xffffffffu, c1 >= cut);
+            const uint32_t B2 = __ballot_sync(0xffffffffu, c2 >= cut), B3 = __ballot_sync(0xffffffffu, c3 >= cut);
+            const uint32_t B4 = __ballot_sync(0xffffffffu, c4 >= cut);
 
-            // survivors keep candidate order: steps (slot-major, base-minor), then stays
-            const bool f0 = c0 >= cut, f1 = c1 >= cut, f2 = c2 >= cut, f3 = c3 >= cut, f4 = c4 >= cut;
-            const uint32_t B0 = __ballot_sync(0xffffffffu, f0), B1 = __ballot_sync(0xffffffffu, f1);
-            const uint32_t B2 = __ballot_sync(0xffffffffu, f2), B3 = __ballot_sync(0xffffffffu, f3);
-            const uint32_t B4 = __ballot_sync(0xffffffffu, f4);
-            int p = __popc(B0 & lt_mask) + __popc(B1 & lt_mask) + __popc(B2 & lt_mask) + __popc(B3 & lt_mask);
-            const int nsteps = __popc(B0) + __popc(B1) + __popc(B2) + __popc(B3);
-            const int base_state = (state << 2) & (NS - 1);
-            if (f0) { if (p < kBeam) sm.rec[p] = make_uint4(crc_step2(hash, 0), base_state | 0, __float_as_uint(c0), lane | (0 << 6)); ++p; }
-            if (f1) { if (p < kBeam) sm.rec[p] = make_uint4(crc_step2(hash, 1), base_state | 1, __float_as_uint(c1), lane | (1 << 6)); ++p; }
-            if (f2) { if (p < kBeam) sm.rec[p] = make_uint4(crc_step2(hash, 2), base_state | 2, __float_as_uint(c2), lane | (2 << 6)); ++p; }
-            if (f3) { if (p < kBeam) sm.rec[p] = make_uint4(crc_step2(hash, 3), base_state | 3, __float_as_uint(c3), lane | (3 << 6)); ++p; }
-            const int ps = nsteps + __popc(B4 & lt_mask);
-            if (f4 && ps < kBeam) sm.rec[ps] = make_uint4(hash, state, __float_as_uint(c4), lane | 32 | (b_own << 6));
-            __syncwarp();
-            W = kept;
-            uint32_t meta = 0;
-            if (lane < W) {
-                const uint4 r = sm.rec[lane];
-                hash = r.x;
-                state = (int)r.y;
-                score = __uint_as_float(r.z);
-                meta = r.w;
+            // survivors keep candidate order: steps (slot-major, base-minor), then stays.  Each
+            // survivor drops {score, parent slot | stay | base} at its new slot; the new owner
+            // fetches the parent's hash and k-mer by shuffle and extends them itself.
+            {
+                int p = (__popc(B0 & lt_mask) + __popc(B1 & lt_mask)) + (__popc(B2 & lt_mask) + __popc(B3 & lt_mask));
+                const int nsteps = (__popc(B0) + __popc(B1)) + (__popc(B2) + __popc(B3));
+                // a survivor beyond the 32nd, and every non-survivor, writes into a spare slot
+                // of its own instead of branching around the store
+                const uint32_t bit = 1u << lane;
+                const int spare = kBeam + lane;
+                const bool k0 = (B0 & bit) != 0, k1 = (B1 & bit) != 0, k2 = (B2 & bit) != 0, k3 = (B3 & bit) != 0;
+                const int p0 = p, p1 = p0 + k0, p2 = p1 + k1, p3 = p2 + k2;
+                sm.slot[(k0 && p0 < kBeam) ? p0 : spare] = make_uint2(__float_as_uint(c0), lane | (0u << 6));
+                sm.slot[(k1 && p1 < kBeam) ? p1 : spare] = make_uint2(__float_as_uint(c1), lane | (1u << 6));
+                sm.slot[(k2 && p2 < kBeam) ? p2 : spare] = make_uint2(__float_as_uint(c2), lane | (2u << 6));
+                sm.slot[(k3 && p3 < kBeam) ? p3 : spare] = make_uint2(__float_as_uint(c3), lane | (3u << 6));
+                const int ps = nsteps + __popc(B4 & lt_mask);
+                sm.slot[((B4 & bit) && ps < kBeam) ? ps : spare] = make_uint2(__float_as_uint(c4), lane | 32u | (b_own << 6));
             }
             __syncwarp();
+            W = kept;
+            const uint2 mine = sm.slot[lane];
+            uint32_t meta = lane < W ? mine.y : 0u;
+            const uint32_t ph = __shfl_sync(0xffffffffu, hash, meta & 31u);
+            const int pst = __shfl_sync(0xffffffffu, state, meta & 31u);
+            {
+                const bool live = lane < W, stayed = (meta & 32u) != 0;
+                const uint32_t h_step = crc_step2(ph, meta >> 6);
+                const int s_step = ((pst << 2) & (NS - 1)) | (int)(meta >> 6);
+                score = live ? __uint_as_float(mine.x) : score;
+                hash = live ? (stayed ? ph : h_step) : hash;
+                state = live ? (stayed ? pst : s_step) : state;
+            }
             if (t == T - 1) {
                 // best survivor swaps into slot 0 (src/beam_search.c:398-414)
                 const float sc = lane < W ? score : -INFINITY;
-                const float top_s = ofd::warp_max(sc);
+                const float top_s = warp_max_f32(sc);
                 const uint32_t eq = __ballot_sync(0xffffffffu, lane < W && sc == top_s && sc > -FLT_MAX);
                 const int at = eq ? __ffs(eq) - 1 : 0;
                 const uint32_t h0 = __shfl_sync(0xffffffffu, hash, 0), ha = __shfl_sync(0xffffffffu, hash, at);
@@ -544,7 +613,10 @@ fwd_beam_kernel(const FusedArgs a) {
                 if (lane == at) { hash = h0; state = s0; score = v0; meta = m0_; }
                 if (lane == 0) { hash = ha; state = sa; score = va; meta = ma; }
             }
-            if (lane < W) score = __fsub_rn(score, brow[state]);
+            {
+                const float back = brow[state];
+                score = lane < W ? __fsub_rn(score, back) : score;
+            }
             bp_chunk[(size_t)(t + 1) * kBeam + lane] = (unsigned char)meta;
             __syncwarp();
             if (lane == 0) ofd::mbar_arrive(&sm.empty[slot_a]);
@@ -557,24 +629,49 @@ fwd_beam_kernel(const FusedArgs a) {
     unsigned char *tail = sm.score_ring[0];
     const int Tp = (T + 16) & ~15;
     unsigned char *win = tail;                          // kWin * 32 bytes
-    unsigned char *path = win + kWin * kBeam;           // [T+1] packed back-pointer of the path
+    unsigned char *bexit = win + kWin * kBeam;          // [kWin/8][32] slot reached below an 8-row block
+    int *bentry = reinterpret_cast<int *>(bexit + (kWin / 8) * kBeam);  // [kWin/8] slot entering each block
+    unsigned char *path = reinterpret_cast<unsigned char *>(bentry + kWin / 8);  // [T+1] packed back-pointer of the path
     unsigned char *ext = path + Tp;                     // [SL + T] initial k-mer bases then steps
     unsigned short *cnt = reinterpret_cast<unsigned short *>(ext + Tp + 16);  // [T+1] steps so far
     float *qp = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(cnt) + 2 * Tp);  // [T]
 
-    // traceback from slot 0 of the last row (src/beam_search.c:430-438), window by window
+    // traceback from slot 0 of the last row (src/beam_search.c:430-438), window by window.
+    // Following one pointer per row is a chain of dependent shared-memory reads, so the chain is
+    // shortened eightfold: for every block of 8 rows and each of the 32 slots one could enter it
+    // with, all threads first work out where one leaves it (independent short walks); one thread
+    // then hops block to block; finally all threads replay their block with the known entry.
     int at = 0;
     for (int hi_r = T; hi_r >= 1; hi_r -= kWin) {
         const int lo_r = max(1, hi_r - kWin + 1);
-        const int n16 = (hi_r - lo_r + 1) * 2;  // 16-byte pieces
+        const int rows = hi_r - lo_r + 1;
+        const int nblk = (rows + 7) >> 3;
+        const int n16 = rows * 2;  // 16-byte pieces
         const uint4 *src = reinterpret_cast<const uint4 *>(bp_chunk + (size_t)lo_r * kBeam);
         for (int i = tid; i < n16; i += NT) reinterpret_cast<uint4 *>(win)[i] = __ldcg(src + i);
         __syncthreads();
+        for (int w = tid; w < nblk * kBeam; w += NT) {
+            const int g = w >> 5;
+            int e = w & 31;
+            const int top_r = hi_r - 8 * g, bot_r = max(lo_r, top_r - 7);
+            for (int r = top_r; r >= bot_r; --r) e = win[(r - lo_r) * kBeam + e] & 31;
+            bexit[w] = (unsigned char)e;
+        }
+        __syncthreads();
         if (tid == 0) {
-            for (int r = hi_r; r >= lo_r; --r) {
-                const unsigned char b = win[(r - lo_r) * kBeam + at];
+            for (int g = 0; g < nblk; ++g) {
+                bentry[g] = at;
+                at = bexit[g * kBeam + at];
+            }
+        }
+        __syncthreads();
+        for (int g = tid; g < nblk; g += NT) {
+            int e = bentry[g];
+            const int top_r = hi_r - 8 * g, bot_r = max(lo_r, top_r - 7);
+            for (int r = top_r; r >= bot_r; --r) {
+                const unsigned char b = win[(r - lo_r) * kBeam + e];
                 path[r] = b;
-                at = b & 31;
+                e = b & 31;
             }
         }
         __syncthreads();
@@ -616,19 +713,23 @@ fwd_beam_kernel(const FusedArgs a) {
         for (int i = 0; i < SL; ++i) st = (st << 2) | ext[c + i];
         const int base = st & 3;
         const float *pr = post_chunk + (size_t)r * NS;
-        float prob = __ldcg(pr + st);
         int nb[8];
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
             nb[2 * b] = (st >> 2) + MSB * b;
             nb[2 * b + 1] = ((st << 2) & (NS - 1)) + b;
         }
+        // all nine posteriors are fetched before any is used: one memory round trip, not nine
+        float pv[8];
+        float prob = __ldcg(pr + st);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) pv[k] = __ldcg(pr + nb[k]);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
             bool fresh = nb[k] != st;
 #pragma unroll
             for (int m = 0; m < k; ++m) fresh = fresh && (nb[m] != nb[k]);
-            if (fresh) prob = __fadd_rn(prob, __ldcg(pr + nb[k]));
+            prob = fresh ? __fadd_rn(prob, pv[k]) : prob;
         }
         prob = prob > 1.0f ? 1.0f : (prob < 0.0f ? 0.0f : prob);
         prob = powf(prob, 0.4f);
@@ -689,7 +790,7 @@ cudaError_t launch(const OfFusedLaunch &l, cudaStream_t stream) {
     const int Tp = (l.T + 16) & ~15;
     const size_t ring_bytes = (size_t)RING * (Smem::kScoreRow + Smem::kBwdRow);
     const size_t extra = (l.C != NS * 4) ? (size_t)RING * Smem::kScoreRow : 0;
-    const size_t tail = (size_t)kWin * kBeam + 8 * (size_t)Tp + 64;
+    const size_t tail = (size_t)kWin * kBeam + (kWin / 8) * (kBeam + 4) + 8 * (size_t)Tp + 64;
     size_t bytes = sizeof(Smem) + extra + 128;
     if (tail > ring_bytes + extra) bytes += tail - (ring_bytes + extra);
     if (bytes > 227 * 1024) return cudaErrorInvalidValue;
@@ -713,7 +814,7 @@ cudaError_t launch(const OfFusedLaunch &l, cudaStream_t stream) {
 cudaError_t of_launch_fwd_beam(const OfFusedLaunch &l, cudaStream_t stream) {
     switch (l.state_len) {
         case 3: return launch<64, 1, 8>(l, stream);
-        case 4: return launch<256, 2, 8>(l, stream);
+        case 4: return launch<256, 4, 8>(l, stream);
         case 5: return launch<1024, 2, 6>(l, stream);
         default: return cudaErrorInvalidValue;
     }
