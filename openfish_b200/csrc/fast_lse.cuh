@@ -66,6 +66,38 @@ __device__ __forceinline__ bool lse5_try_fast(const float v[5], float &out) {
 
 namespace ofd {
 
+// K fast evaluations stage by stage.  out[k] is the certified result where ok[k], and otherwise
+// the better of the two candidate floats (the one nearest to max + log(sum) as estimated), to be
+// confirmed or corrected by the value-exact routine.
+template <int K>
+__device__ __forceinline__ void lse5_fast_guess(const float (*v)[5], float *out, bool *ok) {
+    const float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
+    float m[K], e[K][5], s[K], l[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k)
+        m[k] = fmaxf(fmaxf(fmaxf(v[k][0], v[k][1]), fmaxf(v[k][2], v[k][3])), v[k][4]);
+#pragma unroll
+    for (int i = 0; i < 5; ++i)
+#pragma unroll
+        for (int k = 0; k < K; ++k) e[k][i] = ex2_approx((v[k][i] - m[k]) * kLog2e);
+#pragma unroll
+    for (int k = 0; k < K; ++k) s[k] = (((e[k][0] + e[k][1]) + e[k][2]) + e[k][3]) + e[k][4];
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+        const unsigned bits = __float_as_uint(s[k]);
+        const float q = (float)((int)(bits >> 23) - 127);
+        const float f = __uint_as_float((bits & 0x007fffffu) | 0x3f800000u);
+        l[k] = (q + lg2_approx(f)) * kLn2;
+    }
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+        const float lo = m[k] + (l[k] - kLseEps);
+        const float hi = m[k] + (l[k] + kLseEps);
+        out[k] = m[k] + l[k];
+        ok[k] = lo == hi && fabsf(lo) < 3.0e38f;
+    }
+}
+
 // K log-sum-exps for one thread: fast path first, value-exact fallback for the states whose
 // rounding the fast path cannot certify.  When most of the warp needs the fallback (the first
 // few hundred timesteps, where scores are small and the float grid is fine) the batched
