@@ -82,8 +82,8 @@ int openfish_b200_kernels_per_decode(void);
  * malloc or other allocating routine.
  *
  *   - Shapes whose intermediates do not fit are refused with OPENFISH_B200_ERR_SCRATCH_LIMIT:
- *     needed = 2*N*(T+1)*4^state_len*4 + N*(T+1)*32 + N*T*28 bytes (+ 5 KB), e.g. fast T=1666 up
- *     to N=52, hac up to N=14, sup up to N=3.
+ *     needed = 3*N*(T+1)*4^state_len*4 + N*(T+1)*32 + N*T*28 bytes (+ 5 KB), e.g. fast T=1666 up
+ *     to N=36, hac up to N=9, sup up to N=2.
  *   - All calls on one GPU share the array.  It keeps what the previous call left (the call
  *     clears what has to start from zero itself); two calls that overlap on the same GPU race,
  *     so serialise them.

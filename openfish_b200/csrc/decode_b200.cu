@@ -3,7 +3,8 @@
 // Replaces gpubuf_init_cuda / gpubuf_free_cuda / decode_cuda (src/decode_cuda.cu:11-212).
 // Differences in design: the caller-visible openfish_gpubuf_t sits at the start of a private
 // record that also owns a stream, timing events, the arithmetic tables and a page-locked
-// staging area; one decode is two kernel launches and one device-to-host copy, all stream
+// staging area; one decode is two kernel launches (both scans side by side, then posterior + beam
+// search + sequence) and one device-to-host copy, all stream
 // ordered, with a single host wait at the end (the reference launches five kernels and three
 // memsets with a device-wide synchronisation after each and copies with three blocking
 // pageable transfers).
@@ -15,7 +16,7 @@
 #include <string.h>
 
 #include "backend.h"
-#include "bwd_scan.cuh"
+#include "scan.cuh"
 #include "exact_math.cuh"
 #include "fwd_beam.cuh"
 #include "of_device.cuh"
@@ -33,6 +34,7 @@ struct GpuBuf {
     cudaStream_t stream;
     cudaEvent_t ev[4];
     ofx::Tables *d_tables;
+    float *d_fwd;              // forward scores [N][T+1][ns]: scan kernel -> posterior kernel
     int *d_status;
     unsigned char *d_results;  // moves | sequence | qstring, N*T bytes each
     unsigned char *h_stage;    // page-locked, 3*N*T bytes + one status word
@@ -89,6 +91,7 @@ int destroy(GpuBuf *g) {
     cudaFree(g->pub.base_probs);
     cudaFree(g->pub.total_probs);
     cudaFree(g->d_tables);
+    cudaFree(g->d_fwd);
     cudaFree(g->d_status);
     if (g->h_stage) cudaFreeHost(g->h_stage);
     for (int i = 0; i < 4; ++i)
@@ -123,6 +126,7 @@ extern "C" int ofb_gpubuf_create(int T, int N, int state_len, openfish_gpubuf_t 
         // result arrays share one allocation so that one copy brings them back
         CU(cudaMalloc(&g->pub.bwd_NTC, tens));
         CU(cudaMalloc(&g->pub.post_NTC, tens));
+        CU(cudaMalloc(&g->d_fwd, tens));
         CU(cudaMalloc(&g->d_results, 3 * nt));
         g->pub.moves = g->d_results;
         g->pub.sequence = reinterpret_cast<char *>(g->d_results + nt);
@@ -183,12 +187,13 @@ extern "C" int ofb_decode_submit(int T, int N, int C, const void *scores, int st
     const size_t nt = (size_t)N * T;
 
     CU(cudaEventRecord(g->ev[0], g->stream));
-    CU(of_launch_bwd_scan(scores, g->pub.bwd_NTC, T, N, state_len, blank_score, g->d_tables,
-                          g->d_status, g->stream));
+    CU(of_launch_scans(scores, g->pub.bwd_NTC, g->d_fwd, T, N, state_len, blank_score, g->d_tables,
+                       g->d_status, g->stream));
     CU(cudaEventRecord(g->ev[1], g->stream));
     OfFusedLaunch l;
     l.scores_fp16 = scores;
     l.bwd = g->pub.bwd_NTC;
+    l.fwd = g->d_fwd;
     l.post = g->pub.post_NTC;
     l.bp = static_cast<unsigned char *>(g->pub.beam_vector);
     l.moves = g->pub.moves;

@@ -6,7 +6,7 @@
 // device-wide synchronisation a cudaMalloc / cudaFree implies in the middle of its steady
 // state.  openfish_gpubuf_init does ten cudaMallocs, a cudaMallocHost, a stream and four events,
 // and openfish_decode_gpu three host mallocs per call.  The entry point below needs none of
-// that: every intermediate of the decode (backward scores, posteriors, back-pointers, path
+// that: every intermediate of the decode (backward and forward scores, posteriors, back-pointers, path
 // states, per-timestep qualities, the arithmetic tables, the status word) lives in ONE
 // file-scope device array of fixed size, the results go to device buffers the caller owns, the
 // work runs on the legacy default stream, and the only runtime calls are kernel launches,
@@ -26,7 +26,7 @@
 
 #include <mutex>
 
-#include "bwd_scan.cuh"
+#include "scan.cuh"
 #include "exact_math.cuh"
 #include "fwd_beam.cuh"
 #include "of_device.cuh"
@@ -95,12 +95,13 @@ extern "C" int openfish_b200_decode_static(int T, int N, int C, const void *scor
     if (options->beam_width != 32)
         return report(OPENFISH_B200_ERR_OPTION, "beam_width must be 32");
 
-    // carve the array: tables | status | bwd | post | back-pointers | states | qual | probs
+    // carve the array: tables | status | bwd | fwd | post | back-pointers | states | qual | probs
     const size_t nt = (size_t)N * T, rows = (size_t)N * (T + 1);
     size_t off = 0;
     const size_t o_tables = off; off += align_up(sizeof(ofx::Tables));
     const size_t o_status = off; off += 256;
     const size_t o_bwd = off; off += align_up(rows * ns * sizeof(float));
+    const size_t o_fwd = off; off += align_up(rows * ns * sizeof(float));
     const size_t o_post = off; off += align_up(rows * ns * sizeof(float));
     const size_t o_bp = off; off += align_up(rows * 32);
     const size_t o_states = off; off += align_up(nt * sizeof(int));
@@ -126,15 +127,17 @@ extern "C" int openfish_b200_decode_static(int T, int N, int C, const void *scor
     const ofx::Tables *tables = reinterpret_cast<const ofx::Tables *>(base + o_tables);
     int *status = reinterpret_cast<int *>(base + o_status);
     float *bwd = reinterpret_cast<float *>(base + o_bwd);
+    float *fwd = reinterpret_cast<float *>(base + o_fwd);
     cudaStream_t stream = 0;  // legacy default stream: nothing to create
     e = cudaMemsetAsync(status, 0, sizeof(int), stream);  // the one thing that must start at zero
     if (e == cudaSuccess)
-        e = of_launch_bwd_scan(scores_TNC, bwd, T, N, state_len, options->blank_score, tables,
-                               status, stream);
+        e = of_launch_scans(scores_TNC, bwd, fwd, T, N, state_len, options->blank_score, tables,
+                            status, stream);
     if (e == cudaSuccess) {
         OfFusedLaunch l;
         l.scores_fp16 = scores_TNC;
         l.bwd = bwd;
+        l.fwd = fwd;
         l.post = reinterpret_cast<float *>(base + o_post);
         l.bp = base + o_bp;
         l.moves = moves_gpu;

@@ -1,29 +1,30 @@
-// fwd_beam.cu -- forward scan + posterior, beam search, traceback, per-base quality and
-// sequence/qstring generation for one chunk per block, fused in one sm_100a kernel.
+// fwd_beam.cu -- posterior, beam search, traceback, per-base quality and sequence/qstring
+// generation for one chunk per block, fused in one sm_100a kernel.
 //
-// Replaces the reference kernels fwd_post_scan (src/scan_cuda.cu:59-199), beam_search
-// (src/beam_search_cuda.cu:139-528), compute_qual_data (:530-605) and generate_sequence
-// (:52-121).  The beam search follows the reference's CPU routine beam_search_cpu
-// (src/beam_search.c:117-497) -- including its bisection of the pruning threshold, which the
-// reference's CUDA kernel lacks -- because output parity is defined against the CPU decoder.
+// Replaces the softmax half of the reference kernel fwd_post_scan (src/scan_cuda.cu:147-199) and
+// the kernels beam_search (src/beam_search_cuda.cu:139-528), compute_qual_data (:530-605) and
+// generate_sequence (:52-121).  The beam search follows the reference's CPU routine
+// beam_search_cpu (src/beam_search.c:117-497) -- including its bisection of the pruning
+// threshold, which the reference's CUDA kernel lacks -- because output parity is defined against
+// the CPU decoder.  The forward and backward scores come from the scan kernel (scan.cu).
 //
 // Roles inside a block (one chunk):
-//   scan warps   ns/SPT threads, SPT consecutive states each: forward recursion in shared memory
-//                (one named barrier per timestep), in the same value-exact arithmetic as the
-//                backward scan so that fwd+bwd equals the CPU's float for float, and the
-//                posterior softmax of fwd+bwd.  The
-//                softmax needs no per-row maximum: the log partition function is the same for
-//                every row, so one offset taken from row 0 keeps every exponent in range; the
-//                row sum is reduced across warps and applied one timestep late.
-//   beam warp    lane = beam slot (width <= 32).  Everything is warp-synchronous: candidate
-//                scores, duplicate-prefix merges (CRC32C hashes; a stay merges with the step
-//                whose parent hash equals the stay's hash run backwards through the CRC),
-//                maximum, threshold bisection by population counts, order-preserving
-//                compaction by ballots.  One packed back-pointer byte per slot and timestep
-//                goes to HBM (prev slot 5 bits | stay 1 bit | base 2 bits).
-//   copy warp    one lane issues 1-D bulk asynchronous copies (no multicast) of score row t and
-//                backward row t into a ring; both consumers release a ring slot through an
-//                mbarrier.  Scores are read from HBM once for both consumers.
+//   posterior warps  ns/4 threads, four consecutive states each: posterior = softmax over states
+//                of fwd + bwd, row by row (src/decode_cpu.c:115,121-147).  No per-row maximum is
+//                needed: the log partition function is the same for every row, so one offset
+//                taken from row 0 keeps every exponent in range; the row sum is reduced across
+//                warps and applied one timestep late (one named barrier per timestep).
+//   beam warp    lane = beam slot (width <= 32).  Everything is warp-synchronous and, where
+//                lanes differ, branch free: candidate scores, duplicate-prefix merges (CRC32C
+//                hashes; a stay merges with the step whose parent hash equals the stay's hash
+//                run backwards through the CRC), maximum, threshold bisection by warp
+//                reductions, order-preserving compaction by ballots.  One packed back-pointer
+//                byte per slot and timestep goes to HBM (prev slot 5 bits | stay 1 bit | base
+//                2 bits).
+//   copy warp    one lane issues 1-D bulk asynchronous copies (no multicast) of score row t (for
+//                the beam search, timesteps strided by N*C as in src/decode_cpu.c:204,216),
+//                backward row t and forward row t into a ring; both consumers release a ring
+//                slot through an mbarrier.
 // After the last timestep the block walks the back-pointers (staged through shared memory in
 // windows), rebuilds the k-mer of every path element from the emitted bases, gathers the
 // posterior of each path k-mer and its shifted neighbours, and emits moves, sequence and
@@ -64,10 +65,6 @@ __device__ __forceinline__ float fold2(float x, float y, const ofx::TabRef t) {
     const float lo = m + (l - eps), hi = m + (l + eps);
     if (lo == hi && fabsf(lo) < 3.0e38f) return lo;
     return ofx::fold2_exact(x, y, t);
-}
-
-__device__ __forceinline__ float half_bits_to_float(uint32_t w, int odd) {
-    return __half2float(__ushort_as_half((unsigned short)(odd ? (w >> 16) : (w & 0xffffu))));
 }
 
 // CRC32C over two input bits, table form of src/beam_search.c:103-115:
@@ -113,31 +110,6 @@ __device__ __forceinline__ void store_floats(float *p, const float (&d)[SPT]) {
     else if constexpr (SPT == 2) *reinterpret_cast<float2 *>(p) = make_float2(d[0], d[1]);
     else *p = d[0];
 }
-// The 4*SPT fp16 scores of SPT consecutive states (8*SPT contiguous bytes) widened to fp32.
-// For SPT = 4 the two 16-byte halves are read in an order that depends on the thread so that a
-// quarter-warp never hits a bank twice.
-template <int SPT>
-__device__ __forceinline__ void load_scores(float (&sc)[SPT * 4], const unsigned char *p, int u) {
-    uint32_t w[SPT * 2];
-    if constexpr (SPT == 4) {
-        const int sw = (u >> 2) & 1;
-        const uint4 q0 = *reinterpret_cast<const uint4 *>(p + 16 * sw);
-        const uint4 q1 = *reinterpret_cast<const uint4 *>(p + 16 * (1 - sw));
-        const uint4 lo = sw ? q1 : q0, hi = sw ? q0 : q1;
-        w[0] = lo.x; w[1] = lo.y; w[2] = lo.z; w[3] = lo.w; w[4] = hi.x; w[5] = hi.y; w[6] = hi.z; w[7] = hi.w;
-    } else if constexpr (SPT == 2) {
-        const uint4 q = *reinterpret_cast<const uint4 *>(p);
-        w[0] = q.x; w[1] = q.y; w[2] = q.z; w[3] = q.w;
-    } else {
-        const uint2 q = *reinterpret_cast<const uint2 *>(p);
-        w[0] = q.x; w[1] = q.y;
-    }
-#pragma unroll
-    for (int i = 0; i < SPT * 2; ++i) {
-        sc[2 * i] = half_bits_to_float(w[i], 0);
-        sc[2 * i + 1] = half_bits_to_float(w[i], 1);
-    }
-}
 template <int NW>
 __device__ __forceinline__ float sum_partials(const float *p) {
     float s = 0.f;
@@ -158,7 +130,6 @@ template <int NS, int RING>
 struct FusedSmem {
     static constexpr int kScoreRow = NS * 8;  // bytes of one fp16 score row
     static constexpr int kBwdRow = NS * 4;    // bytes of one fp32 backward row
-    alignas(16) float alpha[2][NS];
     alignas(16) float psum[2][32];
     float red[32];
     alignas(16) uint4 rec[kBeam];
@@ -167,7 +138,6 @@ struct FusedSmem {
     unsigned char owner[8192 + 32];    // (+ one spare per lane) hash -> slot + 1 of the beam element owning it (duplicate detection)
     int init_state[kBeam];
     double exp2_j[ofx::kExpTab];
-    alignas(16) double exp2_rep[ofx::kExpTab * 16];  // per-lane copies for the scan warps
     double rcp_c[ofx::kLogTab];
     double log_c[ofx::kLogTab];
     alignas(8) uint64_t full[RING];
@@ -177,11 +147,13 @@ struct FusedSmem {
     // rings last: the tail phase reuses them (and whatever dynamic shared memory follows)
     alignas(128) unsigned char score_ring[RING][kScoreRow];
     alignas(128) unsigned char bwd_ring[RING][kBwdRow];
+    alignas(128) unsigned char fwd_ring[RING][kBwdRow];
 };
 
 struct FusedArgs {
     const __half *scores;  // [T][N][C] fp16
     const float *bwd;      // [N][T+1][ns]
+    const float *fwd;      // [N][T+1][ns]
     float *post;           // [N][T+1][ns]
     unsigned char *bp;     // [N][T+1][32] packed back-pointers
     uint8_t *moves;        // [N][T]
@@ -197,14 +169,14 @@ struct FusedArgs {
     float stay, log_beam_cut, q_shift, q_scale;
 };
 
-template <int NS, int SPT, int RING>
-__global__ void __launch_bounds__((NS / SPT < 32 ? 32 : NS / SPT) + 64)
+template <int NS, int RING>
+__global__ void __launch_bounds__((NS / 4 < 32 ? 32 : NS / 4) + 64)
 fwd_beam_kernel(const FusedArgs a) {
+    constexpr int SPT = 4;  // states per posterior thread
     constexpr int BITS = (NS == 64) ? 6 : (NS == 256 ? 8 : 10);
     constexpr int SL = BITS / 2;
     constexpr int MSB = NS / 4;
-    constexpr int TPC = NS / SPT;               // scan threads that own states (SPT each)
-    static_assert(TPC % 32 == 0, "scan warps must be full: they vote with the full mask");
+    constexpr int TPC = NS / SPT;               // posterior threads that own states (SPT each)
     constexpr int TPAD = TPC < 32 ? 32 : TPC;   // scan threads including idle lanes
     constexpr int NFW = TPAD / 32;              // scan warps
     constexpr int NT = TPAD + 64;
@@ -217,13 +189,7 @@ fwd_beam_kernel(const FusedArgs a) {
     const int lane = tid & 31;
     const int chunk = blockIdx.x;
     const int T = a.T, N = a.N;
-    const bool own_beam_ring = a.C != NS * 4;  // beam search strides timesteps by N*C
-    // the beam search's own ring, when it has one, sits in dynamic shared memory behind the struct
-    unsigned char *beam_ring =
-        own_beam_ring ? reinterpret_cast<unsigned char *>(&sm) + sizeof(Smem) : &sm.score_ring[0][0];
-
     for (int i = tid; i < ofx::kExpTab; i += NT) sm.exp2_j[i] = a.tables->exp2_j[i];
-    for (int i = tid; i < ofx::kExpTab * 16; i += NT) sm.exp2_rep[i] = a.tables->exp2_j[i / 16];
     for (int i = tid; i < ofx::kLogTab; i += NT) {
         sm.rcp_c[i] = a.tables->rcp_c[i];
         sm.log_c[i] = a.tables->log_c[i];
@@ -247,41 +213,30 @@ fwd_beam_kernel(const FusedArgs a) {
     if (warp == NFW + 1) {
         // ------------------------------------------------------------------ copy warp
         if (lane == 0) {
-            const __half *scan_scores = a.scores + (size_t)chunk * NS * 4;  // scan addressing
-            const size_t scan_stride = (size_t)N * NS * 4;
+            // the beam search strides timesteps by N*C (src/decode_cpu.c:204,216)
+            const __half *beam_scores = a.scores + (size_t)chunk * NS * 4;
             const size_t beam_stride = (size_t)N * a.C;
+            const float *fwd_chunk = a.fwd + (size_t)chunk * (size_t)(T + 1) * NS;
             for (int t = 0; t <= T; ++t) {
                 const int slot = t % RING;
                 if (t >= RING)
                     ofd::mbar_wait_bounded(&sm.empty[slot], (uint32_t)(t / RING - 1) & 1u,
                                            &sm.abort_flag, a.status);
                 if (sm.abort_flag) break;
-                uint32_t bytes = Smem::kBwdRow;
-                if (t < T) bytes += Smem::kScoreRow * (own_beam_ring ? 2 : 1);
+                const uint32_t bytes = 2 * Smem::kBwdRow + (t < T ? Smem::kScoreRow : 0);
                 ofd::mbar_arrive_expect_tx(&sm.full[slot], bytes);
-                ofd::bulk_g2s(sm.bwd_ring[slot], bwd_chunk + (size_t)t * NS, Smem::kBwdRow,
-                              &sm.full[slot]);
-                if (t < T) {
-                    ofd::bulk_g2s(sm.score_ring[slot], scan_scores + scan_stride * t,
-                                  Smem::kScoreRow, &sm.full[slot]);
-                    if (own_beam_ring)
-                        ofd::bulk_g2s(beam_ring + (size_t)slot * Smem::kScoreRow,
-                                      scan_scores + beam_stride * t, Smem::kScoreRow,
-                                      &sm.full[slot]);
-                }
+                ofd::bulk_g2s(sm.bwd_ring[slot], bwd_chunk + (size_t)t * NS, Smem::kBwdRow, &sm.full[slot]);
+                ofd::bulk_g2s(sm.fwd_ring[slot], fwd_chunk + (size_t)t * NS, Smem::kBwdRow, &sm.full[slot]);
+                if (t < T)
+                    ofd::bulk_g2s(sm.score_ring[slot], beam_scores + beam_stride * t, Smem::kScoreRow,
+                                  &sm.full[slot]);
             }
         }
     } else if (warp < NFW) {
         // ------------------------------------------------------------------ scan warps
         const int u = tid;
         const bool act = u < TPC;
-        const int s0 = u * SPT;   // this thread's states s0 .. s0+SPT-1
-        const int pj = s0 >> 2;   // their shared predecessors are pj + b*ns/4
-        const ofx::TabRef scan_tr = {sm.exp2_rep + (lane & 15), 16, sm.rcp_c, sm.log_c};
-        if (act) {
-#pragma unroll
-            for (int k = 0; k < SPT; ++k) sm.alpha[0][s0 + k] = 0.f;
-        }
+        const int s0 = u * SPT;  // this thread's states s0 .. s0+SPT-1
         // softmax offset: maximum of fwd+bwd at row 0 (= bwd row 0, fwd is zero there)
         ofd::mbar_wait_bounded(&sm.full[0], 0, &sm.abort_flag, a.status);
         float m0 = -FLT_MAX;
@@ -303,34 +258,15 @@ fwd_beam_kernel(const FusedArgs a) {
         for (int k = 0; k < SPT; ++k) e_prev[k] = 0.f;
         for (int t = 0; t <= T; ++t) {
             const int slot = t % RING;
-            float nw[SPT], e[SPT];
+            float e[SPT];
 #pragma unroll
-            for (int k = 0; k < SPT; ++k) nw[k] = e[k] = 0.f;
+            for (int k = 0; k < SPT; ++k) e[k] = 0.f;
             if (act) {
-                const float *ain = sm.alpha[t & 1];
-                float ow[SPT], bv[SPT], sc[SPT * 4];
-                load_floats<SPT>(ow, ain + s0);
-                const float p0 = ain[pj], p1 = ain[pj + MSB], p2 = ain[pj + 2 * MSB], p3 = ain[pj + 3 * MSB];
+                float fv[SPT], bv[SPT];
+                load_floats<SPT>(fv, reinterpret_cast<const float *>(sm.fwd_ring[slot]) + s0);
                 load_floats<SPT>(bv, reinterpret_cast<const float *>(sm.bwd_ring[slot]) + s0);
-                if (t < T) {
-                    load_scores<SPT>(sc, sm.score_ring[slot] + 8 * s0, u);
-                } else {
 #pragma unroll
-                    for (int i = 0; i < SPT * 4; ++i) sc[i] = 0.f;  // src/decode_cpu.c:99
-                }
-                float v[SPT][5];
-#pragma unroll
-                for (int k = 0; k < SPT; ++k) {
-                    // state s0+k: score columns 4(s0+k) + b
-                    v[k][0] = ow[k] + a.stay;
-                    v[k][1] = p0 + sc[4 * k];
-                    v[k][2] = p1 + sc[4 * k + 1];
-                    v[k][3] = p2 + sc[4 * k + 2];
-                    v[k][4] = p3 + sc[4 * k + 3];
-                    e[k] = ex2_approx(((ow[k] + bv[k]) - m0) * kLog2e);
-                }
-                ofd::lse5_batch<SPT>(v, nw, scan_tr);
-                store_floats<SPT>(&sm.alpha[(t & 1) ^ 1][s0], nw);
+                for (int k = 0; k < SPT; ++k) e[k] = ex2_approx(((fv[k] + bv[k]) - m0) * kLog2e);
             }
             float part = 0.f;
 #pragma unroll
@@ -405,7 +341,7 @@ fwd_beam_kernel(const FusedArgs a) {
             const int slot_a = t % RING, slot_b = (t + 1) % RING;
             // row t was confirmed when it served as "next row" one step ago (or before the loop)
             ofd::mbar_wait_bounded(&sm.full[slot_b], (uint32_t)((t + 1) / RING) & 1u, &sm.abort_flag, a.status);
-            const __half *srow = reinterpret_cast<const __half *>(beam_ring + (size_t)slot_a * Smem::kScoreRow);
+            const __half *srow = reinterpret_cast<const __half *>(sm.score_ring[slot_a]);
             const float *brow = reinterpret_cast<const float *>(sm.bwd_ring[slot_b]);
             const bool act = lane < W;
             const int q = state & (MSB - 1);
@@ -784,27 +720,27 @@ fwd_beam_kernel(const FusedArgs a) {
 
 namespace {
 
-template <int NS, int SPT, int RING>
+template <int NS, int RING>
 cudaError_t launch(const OfFusedLaunch &l, cudaStream_t stream) {
     using Smem = FusedSmem<NS, RING>;
     const int Tp = (l.T + 16) & ~15;
-    const size_t ring_bytes = (size_t)RING * (Smem::kScoreRow + Smem::kBwdRow);
-    const size_t extra = (l.C != NS * 4) ? (size_t)RING * Smem::kScoreRow : 0;
+    const size_t ring_bytes = (size_t)RING * (Smem::kScoreRow + 2 * Smem::kBwdRow);
+    const size_t extra = 0;
     const size_t tail = (size_t)kWin * kBeam + (kWin / 8) * (kBeam + 4) + 8 * (size_t)Tp + 64;
     size_t bytes = sizeof(Smem) + extra + 128;
     if (tail > ring_bytes + extra) bytes += tail - (ring_bytes + extra);
     if (bytes > 227 * 1024) return cudaErrorInvalidValue;
-    auto kern = fwd_beam_kernel<NS, SPT, RING>;
+    auto kern = fwd_beam_kernel<NS, RING>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
     if (e != cudaSuccess) return e;
     FusedArgs a;
     a.scores = static_cast<const __half *>(l.scores_fp16);
-    a.bwd = l.bwd; a.post = l.post; a.bp = l.bp; a.moves = l.moves; a.sequence = l.sequence;
+    a.bwd = l.bwd; a.fwd = l.fwd; a.post = l.post; a.bp = l.bp; a.moves = l.moves; a.sequence = l.sequence;
     a.qstring = l.qstring; a.states = l.states; a.qual = l.qual; a.base_probs = l.base_probs;
     a.total_probs = l.total_probs; a.tables = l.tables; a.status = l.status;
     a.T = l.T; a.N = l.N; a.C = l.C; a.stay = l.stay; a.log_beam_cut = l.log_beam_cut;
     a.q_shift = l.q_shift; a.q_scale = l.q_scale;
-    constexpr int NT = (NS / SPT < 32 ? 32 : NS / SPT) + 64;
+    constexpr int NT = (NS / 4 < 32 ? 32 : NS / 4) + 64;
     kern<<<l.N, NT, bytes, stream>>>(a);
     return cudaGetLastError();
 }
@@ -813,9 +749,9 @@ cudaError_t launch(const OfFusedLaunch &l, cudaStream_t stream) {
 
 cudaError_t of_launch_fwd_beam(const OfFusedLaunch &l, cudaStream_t stream) {
     switch (l.state_len) {
-        case 3: return launch<64, 1, 8>(l, stream);
-        case 4: return launch<256, 4, 8>(l, stream);
-        case 5: return launch<1024, 2, 6>(l, stream);
+        case 3: return launch<64, 8>(l, stream);
+        case 4: return launch<256, 8>(l, stream);
+        case 5: return launch<1024, 6>(l, stream);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -1,4 +1,4 @@
-// fwd_beam.cuh -- launcher of the fused forward/posterior + beam search + sequence kernel
+// fwd_beam.cuh -- launcher of the fused posterior + beam search + sequence kernel
 // (see fwd_beam.cu).
 #pragma once
 #include <cuda_runtime.h>
@@ -8,6 +8,7 @@ namespace ofx { struct Tables; }
 struct OfFusedLaunch {
     const void *scores_fp16;   // [T][N][C] fp16, 16-byte aligned, C % 8 == 0, C >= 4*ns
     const float *bwd;          // [N][T+1][ns], from the backward scan
+    const float *fwd;          // [N][T+1][ns], from the forward scan
     float *post;               // [N][T+1][ns] out
     unsigned char *bp;         // [N][T+1][32] out, packed back-pointers
     uint8_t *moves;            // [N][T] out

@@ -1,0 +1,534 @@
+// scan.cu -- backward and forward scans of the CRF-CTC decode for sm_100a, one launch for both.
+//
+// Replaces the reference kernel bwd_scan (src/scan_cuda.cu:8-57) and the recursion half of
+// fwd_post_scan (src/scan_cuda.cu:59-146), and reproduces the CPU routines backward_scan and
+// forward_scan (src/decode_cpu.c:13-52, 54-119) bit for bit (see exact_math.cuh):
+//   bwd[n][T][s] = 0,  bwd[n][t][s]   = LSE5( bwd[n][t+1][s] + stay, bwd[n][t+1][4j+b] + score[t][n][4(4j+b) + k] )
+//                                       for s = j + k*ns/4
+//   fwd[n][0][s] = 0,  fwd[n][t+1][s] = LSE5( fwd[n][t][s] + stay,   fwd[n][t][j + b*ns/4] + score[t][n][4s + b] )
+//                                       for s = 4j + k                         (b = 0..3 in both)
+// The two recursions do not depend on each other (only the posterior needs both), and one scan
+// alone leaves most of an SM's issue slots empty -- it is a chain of dependent timesteps with
+// three or four chunks per SM -- so both run side by side: the first half of the grid scans
+// backwards, the second half forwards, and the forward scores go to HBM for the kernel that
+// forms the posterior.
+//
+// Shape of a block.  In either direction the four states that share j also share their four
+// neighbour inputs, and their 16 transition scores are one contiguous 32-byte piece of the score
+// row, so nothing is strided.  SPT of those four states go to one thread.  The previous row
+// lives in shared memory (one block barrier per timestep); score rows arrive through a ring of
+// 1-D bulk asynchronous copies tracked by mbarriers (no multicast), issued a ring length ahead
+// by a copy warp of their own.  Output rows go straight to HBM.
+//
+// Neither scan is bound by HBM (each moves T*4ns*2 + (T+1)*ns*4 bytes per chunk); they are bound
+// by the latency of one timestep's dependent arithmetic.
+#include "scan.cuh"
+#include "exact_math.cuh"
+#include "fast_lse.cuh"
+#include "of_device.cuh"
+
+namespace {
+
+constexpr int kExpCopies = 16;  // per-half-warp-lane copies of the 2^(j/64) table
+
+__device__ __forceinline__ float half_of(uint32_t word, int odd) {
+    return __half2float(__ushort_as_half((unsigned short)(odd ? (word >> 16) : (word & 0xffffu))));
+}
+
+// ------------------------------------------------------------------------------------------
+// The two recursions differ only in which states a thread owns, which inputs they share, where
+// their scores sit inside the 32-byte piece, and in the direction of time.
+
+template <int NS>
+struct BwdTopo {
+    static constexpr int NJ = NS / 4;
+    static constexpr bool kForward = false;
+    // thread (j, slot k) owns state j + k*NJ; the four slots share the successors 4j..4j+3
+    __device__ static int state(int j, int k) { return j + k * NJ; }
+    __device__ static void shared_inputs(const float *in, int j, float (&x)[4]) {
+        const float4 v = *reinterpret_cast<const float4 *>(in + 4 * j);
+        x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+    }
+    // score of (slot k, base b) is half number 4b + k of the piece
+    __device__ static int half_index(int k, int b) { return 4 * b + k; }
+    // the same out of the piece held as eight words, slot k0 + k with k0 (a multiple of SPT)
+    // known only at run time: selects instead of strided shared-memory reads
+    template <int SPT>
+    __device__ static float score(const uint32_t (&w)[8], int k0, int k, int b) {
+        if (SPT == 4) return half_of(w[2 * b + (k >> 1)], k & 1);
+        const uint32_t x = (k0 & 2) ? w[2 * b + 1] : w[2 * b];
+        return SPT == 2 ? half_of(x, k) : half_of(x, k0 & 1);
+    }
+    __device__ static int j_of(int s) { return s % NJ; }
+    __device__ static int k_of(int s) { return s / NJ; }
+    // the states of the next row to be computed that read state s of this row, d = 0..3
+    __device__ static int reader(int s, int d) { return (s >> 2) + d * NJ; }
+    // time: step i reads score row T-1-i and produces output row T-1-i; row T is the zero row
+    __device__ static int score_row(int i, int T) { return T - 1 - i; }
+    __device__ static int out_row(int i, int T) { return T - 1 - i; }
+    __device__ static int zero_row(int T) { return T; }
+};
+
+template <int NS>
+struct FwdTopo {
+    static constexpr int NJ = NS / 4;
+    static constexpr bool kForward = true;
+    // thread (j, slot k) owns state 4j + k; the four slots share the predecessors j + b*NJ
+    __device__ static int state(int j, int k) { return 4 * j + k; }
+    __device__ static void shared_inputs(const float *in, int j, float (&x)[4]) {
+#pragma unroll
+        for (int b = 0; b < 4; ++b) x[b] = in[j + b * NJ];
+    }
+    __device__ static int half_index(int k, int b) { return 4 * k + b; }
+    template <int SPT>
+    __device__ static float score(const uint32_t (&w)[8], int k0, int k, int b) {
+        const int c = b >> 1;
+        if (SPT == 4) return half_of(w[2 * k + c], b & 1);
+        if (SPT == 2) return half_of(k0 ? w[4 + 2 * k + c] : w[2 * k + c], b & 1);
+        const uint32_t x = (k0 & 2) ? ((k0 & 1) ? w[6 + c] : w[4 + c]) : ((k0 & 1) ? w[2 + c] : w[c]);
+        return half_of(x, b & 1);
+    }
+    __device__ static int j_of(int s) { return s >> 2; }
+    __device__ static int k_of(int s) { return s & 3; }
+    __device__ static int reader(int s, int d) { return 4 * (s % NJ) + d; }
+    __device__ static int score_row(int i, int) { return i; }
+    __device__ static int out_row(int i, int) { return i + 1; }
+    __device__ static int zero_row(int) { return 0; }
+};
+
+// The five terms of state s: inputs from row `in`, scores from the chunk's score row `row`.
+template <class Topo>
+__device__ __forceinline__ void terms_of(int s, const float *in, const unsigned char *row, float stay,
+                                         float (&v)[5]) {
+    const int j = Topo::j_of(s), k = Topo::k_of(s);
+    const __half *piece = reinterpret_cast<const __half *>(row) + 16 * j;
+    float x[4];
+    Topo::shared_inputs(in, j, x);
+    v[0] = in[s] + stay;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) v[b + 1] = x[b] + __half2float(piece[Topo::half_index(k, b)]);
+}
+
+// Terms of the SPT states (j, k0 .. k0+SPT-1) of one thread.  The 32-byte piece is read as two
+// 16-byte halves in an order that depends on j so that a quarter-warp never hits a bank twice.
+template <class Topo, int SPT>
+__device__ __forceinline__ void thread_terms(const float *in, const unsigned char *row, int j, int k0,
+                                             float stay, float (&v)[SPT][5]) {
+    const int sw = (j >> 2) & 1;
+    const unsigned char *piece = row + 32 * j;
+    const uint4 p0 = *reinterpret_cast<const uint4 *>(piece + 16 * sw);
+    const uint4 p1 = *reinterpret_cast<const uint4 *>(piece + 16 * (1 - sw));
+    const uint4 lo = sw ? p1 : p0, hi = sw ? p0 : p1;
+    float x[4];
+    Topo::shared_inputs(in, j, x);
+    const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+    for (int k = 0; k < SPT; ++k) {
+        v[k][0] = in[Topo::state(j, k0 + k)] + stay;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) v[k][b + 1] = x[b] + Topo::template score<SPT>(w, k0, k, b);
+    }
+}
+
+template <class Topo, int SPT>
+__device__ __forceinline__ void thread_store(float *smem_row, float *gmem_row, int j, int k0,
+                                             const float (&res)[SPT], bool to_gmem) {
+    if constexpr (Topo::kForward && SPT == 4) {
+        const float4 v = make_float4(res[0], res[1], res[2], res[3]);
+        *reinterpret_cast<float4 *>(smem_row + 4 * j) = v;
+        if (to_gmem) *reinterpret_cast<float4 *>(gmem_row + 4 * j) = v;
+    } else if constexpr (Topo::kForward && SPT == 2) {
+        const float2 v = make_float2(res[0], res[1]);
+        *reinterpret_cast<float2 *>(smem_row + 4 * j + k0) = v;
+        if (to_gmem) *reinterpret_cast<float2 *>(gmem_row + 4 * j + k0) = v;
+    } else {
+#pragma unroll
+        for (int k = 0; k < SPT; ++k) {
+            smem_row[Topo::state(j, k0 + k)] = res[k];
+            if (to_gmem) gmem_row[Topo::state(j, k0 + k)] = res[k];
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Plain variant: CPB chunks per block; uncertified states are settled within the timestep.
+
+template <int NS, int CPB, int RING>
+struct ScanSmem {
+    static constexpr int kRowBytes = NS * 4 * 2;        // one chunk's score row (fp16)
+    static constexpr int kSlotBytes = kRowBytes * CPB;  // one timestep of the block
+    alignas(128) unsigned char ring[RING][kSlotBytes];
+    alignas(16) float alpha[2][CPB][NS];
+    alignas(16) double exp2_rep[ofx::kExpTab * kExpCopies];
+    double rcp_c[ofx::kLogTab];
+    double log_c[ofx::kLogTab];
+    alignas(8) uint64_t full[RING];
+    int abort_flag;
+};
+
+template <class Topo, int NS, int SPT, int CPB, int RING>
+__device__ __forceinline__ void scan_body(unsigned char *smem_raw, int block, const __half *scores,
+                                          float *out, int T, int N, float stay,
+                                          const ofx::Tables *tables, int *status) {
+    constexpr int NJ = NS / 4;
+    constexpr int TPC = NS / SPT;
+    static_assert(TPC % 32 == 0, "a warp must not straddle two chunks");
+    using Smem = ScanSmem<NS, CPB, RING>;
+    Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+
+    const int tid = threadIdx.x;
+    const int cl = tid / TPC;
+    const int j = tid % NJ;
+    const int k0 = ((tid % TPC) / NJ) * SPT;
+    const int chunk0 = block * CPB;
+    const int nlive = min(CPB, N - chunk0);
+    const uint32_t slot_bytes = (uint32_t)nlive * Smem::kRowBytes;
+
+    for (int i = tid; i < ofx::kExpTab * kExpCopies; i += blockDim.x)
+        sm.exp2_rep[i] = tables->exp2_j[i / kExpCopies];
+    for (int i = tid; i < ofx::kLogTab; i += blockDim.x) {
+        sm.rcp_c[i] = tables->rcp_c[i];
+        sm.log_c[i] = tables->log_c[i];
+    }
+    for (int i = tid; i < CPB * NS; i += blockDim.x) (&sm.alpha[0][0][0])[i] = 0.f;
+    if (tid == 0) {
+        sm.abort_flag = 0;
+        for (int r = 0; r < RING; ++r) ofd::mbar_init(&sm.full[r], 1);
+        ofd::mbar_fence_init();
+    }
+    __syncthreads();
+
+    // the scans address scores as [T][N][4ns] whatever C is (src/decode_cpu.c:16-18,27,59-62,80)
+    const size_t t_stride = (size_t)N * NS * 4;
+    const __half *blk_scores = scores + (size_t)chunk0 * NS * 4;
+
+    if (tid >= TPC * CPB) {
+        // ------------------------------------------------------------------ copy warp
+        // Keeps the ring full and takes every mbarrier operation off the scan warps: before it
+        // joins the barrier that ends timestep i it has seen row i+1 land, so the barrier hands
+        // that knowledge (and the data) to everybody; after it the slot of row i is refilled.
+        const bool issuer = tid == TPC * CPB;
+        if (issuer) {
+            for (int i = 0; i < RING && i < T; ++i) {
+                ofd::mbar_arrive_expect_tx(&sm.full[i], slot_bytes);
+                ofd::bulk_g2s(sm.ring[i], blk_scores + t_stride * (size_t)Topo::score_row(i, T), slot_bytes,
+                              &sm.full[i]);
+            }
+            if (T > 0) ofd::mbar_wait_bounded(&sm.full[0], 0u, &sm.abort_flag, status);
+        }
+        __syncthreads();
+        for (int i = 0; i < T; ++i) {
+            if (issuer && i + 1 < T)
+                ofd::mbar_wait_bounded(&sm.full[(i + 1) % RING], (uint32_t)((i + 1) / RING) & 1u,
+                                       &sm.abort_flag, status);
+            __syncthreads();
+            if (issuer && i + RING < T) {
+                const int slot = i % RING;
+                ofd::mbar_arrive_expect_tx(&sm.full[slot], slot_bytes);
+                ofd::bulk_g2s(sm.ring[slot], blk_scores + t_stride * (size_t)Topo::score_row(i + RING, T),
+                              slot_bytes, &sm.full[slot]);
+            }
+        }
+        return;
+    }
+
+    const int chunk = chunk0 + cl;
+    const bool live = chunk < N;
+    const ofx::TabRef tr = {sm.exp2_rep + (tid & (kExpCopies - 1)), kExpCopies, sm.rcp_c, sm.log_c};
+    float *out_chunk = out + (size_t)(live ? chunk : 0) * (size_t)(T + 1) * NS;
+    if (live) {
+#pragma unroll
+        for (int k = 0; k < SPT; ++k) out_chunk[(size_t)Topo::zero_row(T) * NS + Topo::state(j, k0 + k)] = 0.f;
+    }
+    __syncthreads();
+
+    for (int i = 0; i < T; ++i) {
+        float res[SPT];
+#pragma unroll
+        for (int k = 0; k < SPT; ++k) res[k] = 0.f;
+        if (live) {  // a padding chunk of the last block has no data to work on
+            float v[SPT][5];
+            thread_terms<Topo, SPT>(sm.alpha[i & 1][cl], sm.ring[i % RING] + cl * Smem::kRowBytes, j, k0, stay, v);
+            ofd::lse5_batch<SPT>(v, res, tr);
+        }
+        thread_store<Topo, SPT>(sm.alpha[(i & 1) ^ 1][cl], out_chunk + (size_t)Topo::out_row(i, T) * NS, j, k0,
+                                res, live);
+        __syncthreads();  // row complete; the copy warp has confirmed the next score row
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Speculative variant (one chunk per block).
+//
+// In the plain variant a state whose rounding the fp32 evaluation cannot certify sends its whole
+// warp through the value-exact routine before the timestep can end, and almost every timestep
+// has a few such states: the exact routine's latency is paid on nearly every step.  Here the
+// scan warps do not wait for it.  An uncertified state gets the likelier of its two candidate
+// floats and is put on a list; while the scan warps work on the next timestep, a checker warp
+// recomputes the listed states exactly.  If every guess was right (about three timesteps in
+// four) nothing else happens.  If one was wrong the block pauses at the end of that next
+// timestep: the checker corrects the value and recomputes exactly the five states of the next
+// row that read it (the state itself and its four readers) before anybody reads those, and the
+// scan carries on.  (Letting the scan run on and chasing the consequences a step behind does
+// not work: a one-ulp change of an input moves an output by one ulp with a probability equal to
+// that input's weight in the sum, and the weights of a state over its five readers add up to
+// about one, so corrections would breed as fast as they die.)  What reaches HBM is, value for
+// value, what the exact routine alone would have produced.  Three row buffers rotate so that the
+// inputs of a timestep are still there while it is being checked, and score rows are released
+// one timestep late.
+template <int NS, int SPT, int RING>
+struct SpecSmem {
+    static constexpr int kRowBytes = NS * 4 * 2;
+    static constexpr int NW = NS / SPT / 32;  // scan warps
+    static constexpr int kPerWarp = 8;        // listed states per warp and timestep, at most
+    alignas(128) unsigned char ring[RING][kRowBytes];
+    alignas(16) float alpha[3][NS];
+    alignas(16) double exp2_rep[ofx::kExpTab * kExpCopies];
+    double rcp_c[ofx::kLogTab];
+    double log_c[ofx::kLogTab];
+    alignas(8) uint64_t full[RING];
+    unsigned short listed[2][NW][kPerWarp];
+    int n_listed[2][NW];
+    int n_wrong[2];
+    unsigned short wrong_state[NW * kPerWarp];
+    float wrong_value[NW * kPerWarp];
+    int abort_flag;
+};
+
+template <class Topo, int NS, int SPT, int RING>
+__device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, const __half *scores,
+                                          float *out, int T, int N, float stay,
+                                          const ofx::Tables *tables, int *status) {
+    constexpr int NJ = NS / 4;
+    constexpr int TPC = NS / SPT;
+    using Smem = SpecSmem<NS, SPT, RING>;
+    constexpr int NW = Smem::NW, PER = Smem::kPerWarp;
+    static_assert(TPC % 32 == 0, "scan warps must be full");
+    Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int i = tid; i < ofx::kExpTab * kExpCopies; i += blockDim.x)
+        sm.exp2_rep[i] = tables->exp2_j[i / kExpCopies];
+    for (int i = tid; i < ofx::kLogTab; i += blockDim.x) {
+        sm.rcp_c[i] = tables->rcp_c[i];
+        sm.log_c[i] = tables->log_c[i];
+    }
+    for (int i = tid; i < 2 * NW; i += blockDim.x) (&sm.n_listed[0][0])[i] = 0;
+    for (int i = tid; i < NS; i += blockDim.x) sm.alpha[0][i] = 0.f;
+    if (tid == 0) {
+        sm.abort_flag = 0;
+        sm.n_wrong[0] = sm.n_wrong[1] = 0;
+        for (int r = 0; r < RING; ++r) ofd::mbar_init(&sm.full[r], 1);
+        ofd::mbar_fence_init();
+    }
+    __syncthreads();
+
+    const size_t t_stride = (size_t)N * NS * 4;
+    const __half *chunk_scores = scores + (size_t)chunk * NS * 4;
+    float *out_chunk = out + (size_t)chunk * (size_t)(T + 1) * NS;
+    const ofx::TabRef tr = {sm.exp2_rep + (tid & (kExpCopies - 1)), kExpCopies, sm.rcp_c, sm.log_c};
+
+    if (warp == NW) {
+        // ------------------------------------------------------------------ copy warp
+        // A slot is refilled one timestep late: the checker still reads the scores of the
+        // timestep it is checking.
+        const bool issuer = lane == 0;
+        if (issuer) {
+            for (int i = 0; i < RING && i < T; ++i) {
+                ofd::mbar_arrive_expect_tx(&sm.full[i], Smem::kRowBytes);
+                ofd::bulk_g2s(sm.ring[i], chunk_scores + t_stride * (size_t)Topo::score_row(i, T),
+                              Smem::kRowBytes, &sm.full[i]);
+            }
+            if (T > 0) ofd::mbar_wait_bounded(&sm.full[0], 0u, &sm.abort_flag, status);
+        }
+        __syncthreads();
+        for (int i = 0; i < T; ++i) {
+            if (issuer && i + 1 < T)
+                ofd::mbar_wait_bounded(&sm.full[(i + 1) % RING], (uint32_t)((i + 1) / RING) & 1u,
+                                       &sm.abort_flag, status);
+            __syncthreads();
+            if (sm.n_wrong[i & 1]) __syncthreads();
+            if (issuer && i >= 1 && i - 1 + RING < T) {
+                const int slot = (i - 1) % RING;
+                ofd::mbar_arrive_expect_tx(&sm.full[slot], Smem::kRowBytes);
+                ofd::bulk_g2s(sm.ring[slot], chunk_scores + t_stride * (size_t)Topo::score_row(i - 1 + RING, T),
+                              Smem::kRowBytes, &sm.full[slot]);
+            }
+        }
+        return;
+    }
+
+    if (warp == NW + 1) {
+        // ------------------------------------------------------------------ checker warp
+        __syncthreads();  // start of the scan
+        for (int i = 0; i <= T; ++i) {
+            // During timestep i (for i = T: after the last one) check the states listed during
+            // timestep i-1: inputs alpha[(i-1)%3], scores in slot (i-1)%RING, guesses in
+            // alpha[i%3] and in the output row of timestep i-1.
+            int nw = 0;
+            if (i >= 1) {
+                const int par = (i - 1) & 1;
+                int total = 0;
+#pragma unroll
+                for (int w = 0; w < NW; ++w) total += sm.n_listed[par][w];
+                for (int base = 0; base < total; base += 32) {
+                    const int e = base + lane;
+                    int s = 0, acc = 0;
+#pragma unroll
+                    for (int w = 0; w < NW; ++w) {
+                        const int c = sm.n_listed[par][w];
+                        if (e >= acc && e < acc + c) s = sm.listed[par][w][e - acc];
+                        acc += c;
+                    }
+                    float v[5];
+                    terms_of<Topo>(s, sm.alpha[(i - 1) % 3], sm.ring[(i - 1) % RING], stay, v);
+                    const float x = ofx::lse5_exact(v, tr);
+                    const bool wrong = e < total && __float_as_uint(x) != __float_as_uint(sm.alpha[i % 3][s]);
+                    const uint32_t wm = __ballot_sync(0xffffffffu, wrong);
+                    if (wrong) {
+                        const int at = nw + __popc(wm & ((1u << lane) - 1u));
+                        sm.wrong_state[at] = (unsigned short)s;
+                        sm.wrong_value[at] = x;
+                    }
+                    nw += __popc(wm);
+                }
+                __syncwarp();
+            }
+            if (i == T) {
+                // the last row: nobody reads it any more, just correct it
+                float *row = out_chunk + (size_t)Topo::out_row(T - 1, T) * NS;
+                for (int e = lane; e < nw; e += 32) row[sm.wrong_state[e]] = sm.wrong_value[e];
+                break;
+            }
+            if (lane == 0) sm.n_wrong[i & 1] = nw;
+            __syncthreads();  // end of timestep i
+            if (nw) {
+                float *prev_row = out_chunk + (size_t)Topo::out_row(i - 1, T) * NS;
+                for (int e = lane; e < nw; e += 32) {
+                    const int s = sm.wrong_state[e];
+                    sm.alpha[i % 3][s] = sm.wrong_value[e];
+                    prev_row[s] = sm.wrong_value[e];
+                }
+                __syncwarp();
+                // the five states of timestep i's row that read a corrected value
+                float *this_row = out_chunk + (size_t)Topo::out_row(i, T) * NS;
+                for (int idx = lane; idx < 5 * nw; idx += 32) {
+                    const int s = sm.wrong_state[idx / 5], d = idx % 5;
+                    const int dep = d == 4 ? s : Topo::reader(s, d);
+                    float v[5];
+                    terms_of<Topo>(dep, sm.alpha[i % 3], sm.ring[i % RING], stay, v);
+                    const float x = ofx::lse5_exact(v, tr);
+                    sm.alpha[(i + 1) % 3][dep] = x;
+                    this_row[dep] = x;
+                }
+                __syncthreads();  // corrections in place
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------------- scan warps
+    const int j = tid % NJ;
+    const int k0 = (tid / NJ) * SPT;
+#pragma unroll
+    for (int k = 0; k < SPT; ++k) out_chunk[(size_t)Topo::zero_row(T) * NS + Topo::state(j, k0 + k)] = 0.f;
+    __syncthreads();
+    const uint32_t lt_mask = (1u << lane) - 1u;
+    for (int i = 0; i < T; ++i) {
+        float v[SPT][5], res[SPT];
+        bool ok[SPT];
+        // (the stay term is read from the row, not kept in a register: the checker may have
+        // corrected it)
+        thread_terms<Topo, SPT>(sm.alpha[i % 3], sm.ring[i % RING], j, k0, stay, v);
+        ofd::lse5_fast_guess<SPT>(v, res, ok);
+        uint32_t bad[SPT];
+        int total = 0;
+#pragma unroll
+        for (int k = 0; k < SPT; ++k) {
+            bad[k] = __ballot_sync(0xffffffffu, !ok[k]);
+            total += __popc(bad[k]);
+        }
+        if (total > PER) {
+            // many uncertified states (the first few hundred timesteps, where scores are small
+            // and the float grid fine): settle them here and now, nothing to check later
+            ofd::lse5_batch<SPT>(v, res, tr);
+            total = 0;
+        } else if (total) {
+            int base = 0;
+#pragma unroll
+            for (int k = 0; k < SPT; ++k) {
+                if (!ok[k]) sm.listed[i & 1][warp][base + __popc(bad[k] & lt_mask)] = (unsigned short)Topo::state(j, k0 + k);
+                base += __popc(bad[k]);
+            }
+        }
+        if (lane == 0) sm.n_listed[i & 1][warp] = total;
+        thread_store<Topo, SPT>(sm.alpha[(i + 1) % 3], out_chunk + (size_t)Topo::out_row(i, T) * NS, j, k0, res, true);
+        __syncthreads();
+        if (sm.n_wrong[i & 1]) __syncthreads();  // the checker is correcting this row's readers
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// One grid for both directions: blocks [0, nblk) scan backwards, blocks [nblk, 2 nblk) forwards.
+
+template <int NS, int SPT, int CPB, int RING>
+__global__ void __launch_bounds__((NS / SPT) * CPB + 32)
+scan_kernel(const __half *__restrict__ scores, float *__restrict__ bwd, float *__restrict__ fwd,
+            int T, int N, int nblk, float stay, const ofx::Tables *__restrict__ tables, int *status) {
+    extern __shared__ unsigned char smem_raw[];
+    if ((int)blockIdx.x < nblk)
+        scan_body<BwdTopo<NS>, NS, SPT, CPB, RING>(smem_raw, blockIdx.x, scores, bwd, T, N, stay, tables, status);
+    else
+        scan_body<FwdTopo<NS>, NS, SPT, CPB, RING>(smem_raw, blockIdx.x - nblk, scores, fwd, T, N, stay, tables, status);
+}
+
+template <int NS, int SPT, int RING>
+__global__ void __launch_bounds__(NS / SPT + 64)
+scan_spec_kernel(const __half *__restrict__ scores, float *__restrict__ bwd, float *__restrict__ fwd,
+                 int T, int N, float stay, const ofx::Tables *__restrict__ tables, int *status) {
+    extern __shared__ unsigned char smem_raw[];
+    if ((int)blockIdx.x < N)
+        spec_body<BwdTopo<NS>, NS, SPT, RING>(smem_raw, blockIdx.x, scores, bwd, T, N, stay, tables, status);
+    else
+        spec_body<FwdTopo<NS>, NS, SPT, RING>(smem_raw, blockIdx.x - N, scores, fwd, T, N, stay, tables, status);
+}
+
+template <int NS, int SPT, int CPB, int RING>
+cudaError_t launch(const __half *scores, float *bwd, float *fwd, int T, int N, float stay,
+                   const ofx::Tables *tables, int *status, cudaStream_t stream) {
+    using Smem = ScanSmem<NS, CPB, RING>;
+    const size_t bytes = sizeof(Smem) + 128;
+    auto kern = scan_kernel<NS, SPT, CPB, RING>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) return e;
+    const int nblk = (N + CPB - 1) / CPB;
+    kern<<<fwd ? 2 * nblk : nblk, (NS / SPT) * CPB + 32, bytes, stream>>>(scores, bwd, fwd, T, N, nblk, stay,
+                                                                         tables, status);
+    return cudaGetLastError();
+}
+
+template <int NS, int SPT, int RING>
+cudaError_t launch_spec(const __half *scores, float *bwd, float *fwd, int T, int N, float stay,
+                        const ofx::Tables *tables, int *status, cudaStream_t stream) {
+    using Smem = SpecSmem<NS, SPT, RING>;
+    const size_t bytes = sizeof(Smem) + 128;
+    auto kern = scan_spec_kernel<NS, SPT, RING>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) return e;
+    kern<<<fwd ? 2 * N : N, NS / SPT + 64, bytes, stream>>>(scores, bwd, fwd, T, N, stay, tables, status);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t of_launch_scans(const void *scores_fp16, float *bwd, float *fwd, int T, int N,
+                            int state_len, float stay, const ofx::Tables *tables, int *status,
+                            cudaStream_t stream) {
+    const __half *s = static_cast<const __half *>(scores_fp16);
+    switch (state_len) {
+        case 3: return launch<64, 1, 2, 8>(s, bwd, fwd, T, N, stay, tables, status, stream);
+        case 4: return launch_spec<256, 4, 8>(s, bwd, fwd, T, N, stay, tables, status, stream);
+        case 5: return launch<1024, 2, 1, 6>(s, bwd, fwd, T, N, stay, tables, status, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}

@@ -41,7 +41,7 @@ def test_static_scratch_limit_and_bad_arguments_are_refused(native_lib):
     lib.set_openfish_log_level(0)
     try:
         T, N, sl = 1666, 64, 4   # needs ~220 MB of intermediates: far beyond the 48 MiB array
-        need = 2 * N * (T + 1) * 4 ** sl * 4
+        need = 3 * N * (T + 1) * 4 ** sl * 4
         assert need > of.STATIC_SCRATCH_BYTES
         sc = torch.zeros((T, N, 1024), dtype=torch.float16, device="cuda")
         out = [torch.zeros((N, T), dtype=torch.uint8, device="cuda") for _ in range(3)]
