@@ -60,9 +60,15 @@ void openfish_b200_decode_submit(int T, int N, int C, const void *scores_TNC, in
 void openfish_b200_decode_wait(const openfish_gpubuf_t *gpubuf);
 
 /* Device time, in milliseconds, of the gpubuf's last completed decode, measured with CUDA
- * events on the stream the kernels ran on: ms[0] backward scan kernel, ms[1] fused forward /
- * beam-search / sequence kernel, ms[2] device-to-host copies, ms[3] all of it. */
+ * events on the streams the kernels ran on: ms[0] backward scan kernel, ms[1] everything between
+ * it and the copies (the beam search kernel with the forward scan kernel beside it on a second
+ * stream, then the posterior + traceback + sequence kernel), ms[2] device-to-host copies, ms[3]
+ * all of it. */
 void openfish_b200_last_decode_ms(const openfish_gpubuf_t *gpubuf, float ms[4]);
+
+/* The same four numbers followed by: ms[4] beam search kernel, ms[5] forward scan kernel, ms[6]
+ * posterior + traceback + sequence kernel, ms[7] unused (0). */
+void openfish_b200_last_decode_detail_ms(const openfish_gpubuf_t *gpubuf, float ms[8]);
 
 /* Number of kernels one decode call launches (for benchmark bookkeeping). */
 int openfish_b200_kernels_per_decode(void);

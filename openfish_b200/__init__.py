@@ -79,8 +79,9 @@ def lib():
         L.openfish_rotary_emb_gpu.argtypes = [vp, vp, vp] + [i] * 8
         L.openfish_decode_cpu.restype = None
         L.openfish_decode_cpu.argtypes = [i, i, i, i, vp, i, C.POINTER(Opt)] + [C.POINTER(vp)] * 3
-        L.openfish_b200_last_decode_ms.restype = None
-        L.openfish_b200_last_decode_ms.argtypes = [C.POINTER(GpuBufStruct), C.POINTER(C.c_float)]
+        for name in ("openfish_b200_last_decode_ms", "openfish_b200_last_decode_detail_ms"):
+            getattr(L, name).restype = None
+            getattr(L, name).argtypes = [C.POINTER(GpuBufStruct), C.POINTER(C.c_float)]
         L.openfish_b200_last_status.restype = i
         L.openfish_b200_error_text.restype = C.c_char_p
         L.openfish_b200_set_error_mode.argtypes = [i]
@@ -137,9 +138,10 @@ class GpuBuf:
         return torch.as_tensor(_DevView(getattr(self.ptr.contents, name), *spec), device="cuda")
 
     def last_decode_ms(self):
-        ms = (C.c_float * 4)()
-        lib().openfish_b200_last_decode_ms(self.ptr, ms)
-        return dict(bwd_scan=ms[0], fwd_beam=ms[1], d2h=ms[2], total=ms[3])
+        ms = (C.c_float * 8)()
+        lib().openfish_b200_last_decode_detail_ms(self.ptr, ms)
+        return dict(bwd_scan=ms[0], rest=ms[1], d2h=ms[2], total=ms[3], beam_search=ms[4],
+                    fwd_scan=ms[5], posterior_seq=ms[6])
 
 
 def gpubuf_init(T, N, state_len):

@@ -12,7 +12,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libopenfish.so")
-CU = ["scan.cu", "fwd_beam.cu", "rotary.cu", "decode_b200.cu", "decode_static.cu"]
+CU = ["scan.cu", "beam_search.cu", "posterior_seq.cu", "rotary.cu", "decode_b200.cu", "decode_static.cu"]
 CC = ["openfish_api.c"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -25,7 +25,7 @@ int ofb_decode_submit(int T, int N, int C, const void *scores, int state_len, fl
                       char *qstring);
 /* Wait for the gpubuf's decode in flight; returns its status (device-side status included). */
 int ofb_decode_wait(const openfish_gpubuf_t *gpubuf);
-int ofb_last_decode_ms(const openfish_gpubuf_t *gpubuf, float ms[4]);
+int ofb_last_decode_ms(const openfish_gpubuf_t *gpubuf, float ms[8]);
 
 int ofb_rotary(void *x, const void *sin_t, const void *cos_t, int batch, int seqlen, int nheads,
                int rotary_half, long long stride_batch, long long stride_seq,

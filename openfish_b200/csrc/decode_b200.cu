@@ -2,9 +2,10 @@
 //
 // Replaces gpubuf_init_cuda / gpubuf_free_cuda / decode_cuda (src/decode_cuda.cu:11-212).
 // Differences in design: the caller-visible openfish_gpubuf_t sits at the start of a private
-// record that also owns a stream, timing events, the arithmetic tables and a page-locked
-// staging area; one decode is two kernel launches (both scans side by side, then posterior + beam
-// search + sequence) and one device-to-host copy, all stream
+// record that also owns two streams, events, the arithmetic tables and a page-locked staging
+// area; one decode is four kernel launches -- backward scan; beam search with the forward scan
+// beside it on the second stream; posterior + traceback + sequence -- and one device-to-host
+// copy, all stream
 // ordered, with a single host wait at the end (the reference launches five kernels and three
 // memsets with a device-wide synchronisation after each and copies with three blocking
 // pageable transfers).
@@ -18,7 +19,7 @@
 #include "backend.h"
 #include "scan.cuh"
 #include "exact_math.cuh"
-#include "fwd_beam.cuh"
+#include "beam_post.cuh"
 #include "of_device.cuh"
 #include "openfish_b200.h"
 #include "rotary.cuh"
@@ -31,8 +32,11 @@ struct GpuBuf {
     openfish_gpubuf_t pub;  // must stay first: the public pointer is the record's address
     uint32_t magic;
     int T, N, state_len, device;
-    cudaStream_t stream;
-    cudaEvent_t ev[4];
+    cudaStream_t stream;   // everything but the forward scan; blocking, see ofb_gpubuf_create
+    cudaStream_t stream2;  // the forward scan, ordered against `stream` by events only
+    cudaEvent_t ev[7];     // 0 start, 1 bwd scan done, 2 beam search done, 3 sequence done, 4 copies done,
+                           // 5 fwd scan start, 6 fwd scan done
+    int *d_init_kmers;     // inside the beam_vector allocation, behind the back-pointers
     ofx::Tables *d_tables;
     float *d_fwd;              // forward scores [N][T+1][ns]: scan kernel -> posterior kernel
     int *d_status;
@@ -44,7 +48,7 @@ struct GpuBuf {
     uint8_t *dst_moves;
     char *dst_sequence, *dst_qstring;
     bool via_stage;
-    float ms[4];
+    float ms[8];
 };
 
 thread_local char g_err[512] = "";
@@ -82,6 +86,7 @@ bool host_is_pinned(const void *p) {
 int destroy(GpuBuf *g) {
     if (!g) return OPENFISH_B200_OK;
     if (g->pending && g->stream) cudaStreamSynchronize(g->stream);
+    if (g->pending && g->stream2) cudaStreamSynchronize(g->stream2);
     cudaFree(g->pub.bwd_NTC);
     cudaFree(g->pub.post_NTC);
     cudaFree(g->d_results);
@@ -94,8 +99,9 @@ int destroy(GpuBuf *g) {
     cudaFree(g->d_fwd);
     cudaFree(g->d_status);
     if (g->h_stage) cudaFreeHost(g->h_stage);
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < 7; ++i)
         if (g->ev[i]) cudaEventDestroy(g->ev[i]);
+    if (g->stream2) cudaStreamDestroy(g->stream2);
     if (g->stream) cudaStreamDestroy(g->stream);
     g->magic = 0;
     free(g);
@@ -121,7 +127,8 @@ extern "C" int ofb_gpubuf_create(int T, int N, int state_len, openfish_gpubuf_t 
         // a blocking stream: ordered after work the caller queued on the legacy default
         // stream (where the reference runs), so freshly written scores are seen
         CU(cudaStreamCreateWithFlags(&g->stream, cudaStreamDefault));
-        for (int i = 0; i < 4; ++i) CU(cudaEventCreate(&g->ev[i]));
+        CU(cudaStreamCreateWithFlags(&g->stream2, cudaStreamNonBlocking));
+        for (int i = 0; i < 7; ++i) CU(cudaEventCreate(&g->ev[i]));
         // same ten buffers and sizes as the reference (src/decode_cuda.cu:22-45); the three
         // result arrays share one allocation so that one copy brings them back
         CU(cudaMalloc(&g->pub.bwd_NTC, tens));
@@ -131,7 +138,11 @@ extern "C" int ofb_gpubuf_create(int T, int N, int state_len, openfish_gpubuf_t 
         g->pub.moves = g->d_results;
         g->pub.sequence = reinterpret_cast<char *>(g->d_results + nt);
         g->pub.qstring = reinterpret_cast<char *>(g->d_results + 2 * nt);
+        // reference-sized (8 bytes per beam slot and timestep); this library uses 1 byte of the 8
+        // for its packed back-pointers and 128 bytes per chunk behind them for the initial k-mers
         CU(cudaMalloc(&g->pub.beam_vector, (size_t)8 * N * 32 * (T + 1)));
+        g->d_init_kmers = reinterpret_cast<int *>(static_cast<unsigned char *>(g->pub.beam_vector) +
+                                                  (((size_t)N * 32 * (T + 1) + 255) & ~(size_t)255));
         CU(cudaMalloc(&g->pub.states, sizeof(int32_t) * nt));
         CU(cudaMalloc(&g->pub.qual_data, sizeof(float) * nt * 4));
         CU(cudaMalloc(&g->pub.base_probs, sizeof(float) * nt));
@@ -186,32 +197,44 @@ extern "C" int ofb_decode_submit(int T, int N, int C, const void *scores, int st
     if (dev != g->device) return fail(OPENFISH_B200_ERR_ARGUMENT, "gpubuf belongs to device %d, current device is %d", g->device, dev);
     const size_t nt = (size_t)N * T;
 
+    OfDecodeArgs a;
+    a.scores = static_cast<const __half *>(scores);
+    a.bwd = g->pub.bwd_NTC;
+    a.fwd = g->d_fwd;
+    a.post = g->pub.post_NTC;
+    a.bp = static_cast<unsigned char *>(g->pub.beam_vector);
+    a.init_kmers = g->d_init_kmers;
+    a.moves = g->pub.moves;
+    a.sequence = g->pub.sequence;
+    a.qstring = g->pub.qstring;
+    a.states = static_cast<int *>(g->pub.states);
+    a.qual = g->pub.qual_data;
+    a.base_probs = g->pub.base_probs;
+    a.total_probs = g->pub.total_probs;
+    a.tables = g->d_tables;
+    a.status = g->d_status;
+    a.T = T; a.N = N; a.C = C; a.state_len = state_len;
+    a.stay = blank_score;
+    a.log_beam_cut = beam_cut > 0.0f ? logf(beam_cut) : 3.402823466e+38f;  // src/beam_search.c:135
+    a.q_shift = q_shift;
+    a.q_scale = q_scale;
+
+    // stream:  backward scan -> beam search ----------------------> posterior + sequence -> copies
+    // stream2:                  forward scan (beside the beam search) --^
     CU(cudaEventRecord(g->ev[0], g->stream));
-    CU(of_launch_scans(scores, g->pub.bwd_NTC, g->d_fwd, T, N, state_len, blank_score, g->d_tables,
+    CU(of_launch_scans(scores, g->pub.bwd_NTC, nullptr, T, N, state_len, blank_score, g->d_tables,
                        g->d_status, g->stream));
     CU(cudaEventRecord(g->ev[1], g->stream));
-    OfFusedLaunch l;
-    l.scores_fp16 = scores;
-    l.bwd = g->pub.bwd_NTC;
-    l.fwd = g->d_fwd;
-    l.post = g->pub.post_NTC;
-    l.bp = static_cast<unsigned char *>(g->pub.beam_vector);
-    l.moves = g->pub.moves;
-    l.sequence = g->pub.sequence;
-    l.qstring = g->pub.qstring;
-    l.states = static_cast<int *>(g->pub.states);
-    l.qual = g->pub.qual_data;
-    l.base_probs = g->pub.base_probs;
-    l.total_probs = g->pub.total_probs;
-    l.tables = g->d_tables;
-    l.status = g->d_status;
-    l.T = T; l.N = N; l.C = C; l.state_len = state_len;
-    l.stay = blank_score;
-    l.log_beam_cut = beam_cut > 0.0f ? logf(beam_cut) : 3.402823466e+38f;  // src/beam_search.c:135
-    l.q_shift = q_shift;
-    l.q_scale = q_scale;
-    CU(of_launch_fwd_beam(l, g->stream));
+    CU(cudaStreamWaitEvent(g->stream2, g->ev[1], 0));
+    CU(cudaEventRecord(g->ev[5], g->stream2));
+    CU(of_launch_scans(scores, nullptr, g->d_fwd, T, N, state_len, blank_score, g->d_tables,
+                       g->d_status, g->stream2));
+    CU(cudaEventRecord(g->ev[6], g->stream2));
+    CU(of_launch_beam_search(a, g->stream));
     CU(cudaEventRecord(g->ev[2], g->stream));
+    CU(cudaStreamWaitEvent(g->stream, g->ev[6], 0));
+    CU(of_launch_posterior_seq(a, g->stream));
+    CU(cudaEventRecord(g->ev[3], g->stream));
 
     // results: straight into page-locked caller memory, else through the staging area
     g->via_stage = !(host_is_pinned(moves) && host_is_pinned(sequence) && host_is_pinned(qstring));
@@ -223,7 +246,7 @@ extern "C" int ofb_decode_submit(int T, int N, int C, const void *scores, int st
         CU(cudaMemcpyAsync(qstring, g->pub.qstring, nt, cudaMemcpyDeviceToHost, g->stream));
     }
     CU(cudaMemcpyAsync(g->h_status, g->d_status, sizeof(int), cudaMemcpyDeviceToHost, g->stream));
-    CU(cudaEventRecord(g->ev[3], g->stream));
+    CU(cudaEventRecord(g->ev[4], g->stream));
     g->dst_moves = moves;
     g->dst_sequence = sequence;
     g->dst_qstring = qstring;
@@ -247,16 +270,26 @@ extern "C" int ofb_decode_wait(const openfish_gpubuf_t *gpubuf) {
         memcpy(g->dst_sequence, g->h_stage + nt, nt);
         memcpy(g->dst_qstring, g->h_stage + 2 * nt, nt);
     }
+    // ms: 0 backward scan, 1 everything between it and the copies (beam search with the forward
+    // scan beside it, then posterior + sequence), 2 copies, 3 all of it; detail: 4 beam search,
+    // 5 forward scan, 6 posterior + sequence (from the later of its two inputs), 7 unused
     cudaEventElapsedTime(&g->ms[0], g->ev[0], g->ev[1]);
-    cudaEventElapsedTime(&g->ms[1], g->ev[1], g->ev[2]);
-    cudaEventElapsedTime(&g->ms[2], g->ev[2], g->ev[3]);
-    cudaEventElapsedTime(&g->ms[3], g->ev[0], g->ev[3]);
+    cudaEventElapsedTime(&g->ms[1], g->ev[1], g->ev[3]);
+    cudaEventElapsedTime(&g->ms[2], g->ev[3], g->ev[4]);
+    cudaEventElapsedTime(&g->ms[3], g->ev[0], g->ev[4]);
+    cudaEventElapsedTime(&g->ms[4], g->ev[1], g->ev[2]);
+    cudaEventElapsedTime(&g->ms[5], g->ev[5], g->ev[6]);
+    float from_beam = 0.f, from_fwd = 0.f;
+    cudaEventElapsedTime(&from_beam, g->ev[2], g->ev[3]);
+    cudaEventElapsedTime(&from_fwd, g->ev[6], g->ev[3]);
+    g->ms[6] = from_beam < from_fwd ? from_beam : from_fwd;
+    g->ms[7] = 0.f;
     return OPENFISH_B200_OK;
 }
 
-extern "C" int ofb_last_decode_ms(const openfish_gpubuf_t *gpubuf, float ms[4]) {
+extern "C" int ofb_last_decode_ms(const openfish_gpubuf_t *gpubuf, float ms[8]) {
     const GpuBuf *g = priv(gpubuf);
-    for (int i = 0; i < 4; ++i) ms[i] = g->ms[i];
+    for (int i = 0; i < 8; ++i) ms[i] = g->ms[i];
     return OPENFISH_B200_OK;
 }
 

@@ -28,7 +28,7 @@
 
 #include "scan.cuh"
 #include "exact_math.cuh"
-#include "fwd_beam.cuh"
+#include "beam_post.cuh"
 #include "of_device.cuh"
 #include "openfish_b200.h"
 
@@ -104,6 +104,7 @@ extern "C" int openfish_b200_decode_static(int T, int N, int C, const void *scor
     const size_t o_fwd = off; off += align_up(rows * ns * sizeof(float));
     const size_t o_post = off; off += align_up(rows * ns * sizeof(float));
     const size_t o_bp = off; off += align_up(rows * 32);
+    const size_t o_init = off; off += align_up((size_t)N * 32 * sizeof(int));
     const size_t o_states = off; off += align_up(nt * sizeof(int));
     const size_t o_qual = off; off += align_up(nt * 4 * sizeof(float));
     const size_t o_base = off; off += align_up(nt * sizeof(float));
@@ -134,27 +135,29 @@ extern "C" int openfish_b200_decode_static(int T, int N, int C, const void *scor
         e = of_launch_scans(scores_TNC, bwd, fwd, T, N, state_len, options->blank_score, tables,
                             status, stream);
     if (e == cudaSuccess) {
-        OfFusedLaunch l;
-        l.scores_fp16 = scores_TNC;
-        l.bwd = bwd;
-        l.fwd = fwd;
-        l.post = reinterpret_cast<float *>(base + o_post);
-        l.bp = base + o_bp;
-        l.moves = moves_gpu;
-        l.sequence = sequence_gpu;
-        l.qstring = qstring_gpu;
-        l.states = reinterpret_cast<int *>(base + o_states);
-        l.qual = reinterpret_cast<float *>(base + o_qual);
-        l.base_probs = reinterpret_cast<float *>(base + o_base);
-        l.total_probs = reinterpret_cast<float *>(base + o_total);
-        l.tables = tables;
-        l.status = status;
-        l.T = T; l.N = N; l.C = C; l.state_len = state_len;
-        l.stay = options->blank_score;
-        l.log_beam_cut = options->beam_cut > 0.0f ? logf(options->beam_cut) : 3.402823466e+38f;
-        l.q_shift = options->q_shift;
-        l.q_scale = options->q_scale;
-        e = of_launch_fwd_beam(l, stream);
+        OfDecodeArgs a;
+        a.scores = static_cast<const __half *>(scores_TNC);
+        a.bwd = bwd;
+        a.fwd = fwd;
+        a.post = reinterpret_cast<float *>(base + o_post);
+        a.bp = base + o_bp;
+        a.init_kmers = reinterpret_cast<int *>(base + o_init);
+        a.moves = moves_gpu;
+        a.sequence = sequence_gpu;
+        a.qstring = qstring_gpu;
+        a.states = reinterpret_cast<int *>(base + o_states);
+        a.qual = reinterpret_cast<float *>(base + o_qual);
+        a.base_probs = reinterpret_cast<float *>(base + o_base);
+        a.total_probs = reinterpret_cast<float *>(base + o_total);
+        a.tables = tables;
+        a.status = status;
+        a.T = T; a.N = N; a.C = C; a.state_len = state_len;
+        a.stay = options->blank_score;
+        a.log_beam_cut = options->beam_cut > 0.0f ? logf(options->beam_cut) : 3.402823466e+38f;
+        a.q_shift = options->q_shift;
+        a.q_scale = options->q_scale;
+        e = of_launch_beam_search(a, stream);
+        if (e == cudaSuccess) e = of_launch_posterior_seq(a, stream);
     }
     int dev_status = 0;
     if (e == cudaSuccess) e = cudaMemcpy(&dev_status, status, sizeof(int), cudaMemcpyDeviceToHost);

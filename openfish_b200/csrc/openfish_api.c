@@ -185,10 +185,21 @@ void openfish_b200_last_decode_ms(const openfish_gpubuf_t *gpubuf, float ms[4]) 
         raise_error(__func__, OPENFISH_B200_ERR_ARGUMENT, "gpubuf and ms must not be NULL");
         return;
     }
+    float all[8];
+    ofb_last_decode_ms(gpubuf, all);
+    memcpy(ms, all, 4 * sizeof(float));
+}
+
+void openfish_b200_last_decode_detail_ms(const openfish_gpubuf_t *gpubuf, float ms[8]) {
+    clear_error();
+    if (!gpubuf || !ms) {
+        raise_error(__func__, OPENFISH_B200_ERR_ARGUMENT, "gpubuf and ms must not be NULL");
+        return;
+    }
     ofb_last_decode_ms(gpubuf, ms);
 }
 
-int openfish_b200_kernels_per_decode(void) { return 2; }
+int openfish_b200_kernels_per_decode(void) { return 4; }
 
 void openfish_rotary_emb_gpu(void *x_gpu, void *sin_gpu, void *cos_gpu, int batch_size, int seqlen,
                              int nheads, int head_dim, int rotary_half, int stride_batch,

@@ -7,11 +7,10 @@
 //                                       for s = j + k*ns/4
 //   fwd[n][0][s] = 0,  fwd[n][t+1][s] = LSE5( fwd[n][t][s] + stay,   fwd[n][t][j + b*ns/4] + score[t][n][4s + b] )
 //                                       for s = 4j + k                         (b = 0..3 in both)
-// The two recursions do not depend on each other (only the posterior needs both), and one scan
-// alone leaves most of an SM's issue slots empty -- it is a chain of dependent timesteps with
-// three or four chunks per SM -- so both run side by side: the first half of the grid scans
-// backwards, the second half forwards, and the forward scores go to HBM for the kernel that
-// forms the posterior.
+// The two recursions do not depend on each other (only the posterior needs both).  The launcher
+// takes either or both; the decode runs the backward scan first (the beam search waits for it)
+// and the forward scan beside the beam search, which leaves most issue slots free.  Forward
+// scores go to HBM for the kernel that forms the posterior.
 //
 // Shape of a block.  In either direction the four states that share j also share their four
 // neighbour inputs, and their 16 transition scores are one contiguous 32-byte piece of the score
@@ -31,8 +30,11 @@ namespace {
 
 constexpr int kExpCopies = 16;  // per-half-warp-lane copies of the 2^(j/64) table
 
+// One fp16 out of a 32-bit word, widened.  Going through __half2 lets the conversion pick its
+// half of the register directly instead of shifting it out first.
 __device__ __forceinline__ float half_of(uint32_t word, int odd) {
-    return __half2float(__ushort_as_half((unsigned short)(odd ? (word >> 16) : (word & 0xffffu))));
+    const __half2 h = *reinterpret_cast<const __half2 *>(&word);
+    return odd ? __high2float(h) : __low2float(h);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -110,15 +112,14 @@ __device__ __forceinline__ void terms_of(int s, const float *in, const unsigned 
 }
 
 // Terms of the SPT states (j, k0 .. k0+SPT-1) of one thread.  The 32-byte piece is read as two
-// 16-byte halves in an order that depends on j so that a quarter-warp never hits a bank twice.
+// 16-byte halves (a two-way bank conflict, which costs less than the selects that avoid it: the
+// kernel is short of issue slots, not of shared-memory bandwidth).
 template <class Topo, int SPT>
 __device__ __forceinline__ void thread_terms(const float *in, const unsigned char *row, int j, int k0,
                                              float stay, float (&v)[SPT][5]) {
-    const int sw = (j >> 2) & 1;
     const unsigned char *piece = row + 32 * j;
-    const uint4 p0 = *reinterpret_cast<const uint4 *>(piece + 16 * sw);
-    const uint4 p1 = *reinterpret_cast<const uint4 *>(piece + 16 * (1 - sw));
-    const uint4 lo = sw ? p1 : p0, hi = sw ? p0 : p1;
+    const uint4 lo = *reinterpret_cast<const uint4 *>(piece);
+    const uint4 hi = *reinterpret_cast<const uint4 *>(piece + 16);
     float x[4];
     Topo::shared_inputs(in, j, x);
     const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
@@ -417,7 +418,8 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
                     const int dep = d == 4 ? s : Topo::reader(s, d);
                     float v[5];
                     terms_of<Topo>(dep, sm.alpha[i % 3], sm.ring[i % RING], stay, v);
-                    const float x = ofx::lse5_exact(v, tr);
+                    float x;  // certified fp32 evaluation first: it settles all but about 1 in 100
+                    if (!ofd::lse5_try_fast(v, x)) x = ofx::lse5_exact(v, tr);
                     sm.alpha[(i + 1) % 3][dep] = x;
                     this_row[dep] = x;
                 }
@@ -443,10 +445,15 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
         ofd::lse5_fast_guess<SPT>(v, res, ok);
         uint32_t bad[SPT];
         int total = 0;
+        bool all_ok = true;
 #pragma unroll
-        for (int k = 0; k < SPT; ++k) {
-            bad[k] = __ballot_sync(0xffffffffu, !ok[k]);
-            total += __popc(bad[k]);
+        for (int k = 0; k < SPT; ++k) all_ok = all_ok && ok[k];
+        if (__any_sync(0xffffffffu, !all_ok)) {  // about every other timestep per warp
+#pragma unroll
+            for (int k = 0; k < SPT; ++k) {
+                bad[k] = __ballot_sync(0xffffffffu, !ok[k]);
+                total += __popc(bad[k]);
+            }
         }
         if (total > PER) {
             // many uncertified states (the first few hundred timesteps, where scores are small
@@ -469,28 +476,30 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
 }
 
 // ------------------------------------------------------------------------------------------
-// One grid for both directions: blocks [0, nblk) scan backwards, blocks [nblk, 2 nblk) forwards.
+// One grid for either or both directions: the first n_bwd_blocks blocks scan backwards, the
+// rest forwards.
 
 template <int NS, int SPT, int CPB, int RING>
 __global__ void __launch_bounds__((NS / SPT) * CPB + 32)
 scan_kernel(const __half *__restrict__ scores, float *__restrict__ bwd, float *__restrict__ fwd,
-            int T, int N, int nblk, float stay, const ofx::Tables *__restrict__ tables, int *status) {
+            int T, int N, int n_bwd_blocks, float stay, const ofx::Tables *__restrict__ tables, int *status) {
     extern __shared__ unsigned char smem_raw[];
-    if ((int)blockIdx.x < nblk)
+    if ((int)blockIdx.x < n_bwd_blocks)
         scan_body<BwdTopo<NS>, NS, SPT, CPB, RING>(smem_raw, blockIdx.x, scores, bwd, T, N, stay, tables, status);
     else
-        scan_body<FwdTopo<NS>, NS, SPT, CPB, RING>(smem_raw, blockIdx.x - nblk, scores, fwd, T, N, stay, tables, status);
+        scan_body<FwdTopo<NS>, NS, SPT, CPB, RING>(smem_raw, blockIdx.x - n_bwd_blocks, scores, fwd, T, N, stay, tables, status);
 }
 
 template <int NS, int SPT, int RING>
 __global__ void __launch_bounds__(NS / SPT + 64)
 scan_spec_kernel(const __half *__restrict__ scores, float *__restrict__ bwd, float *__restrict__ fwd,
-                 int T, int N, float stay, const ofx::Tables *__restrict__ tables, int *status) {
+                 int T, int N, int n_bwd_blocks, float stay, const ofx::Tables *__restrict__ tables,
+                 int *status) {
     extern __shared__ unsigned char smem_raw[];
-    if ((int)blockIdx.x < N)
+    if ((int)blockIdx.x < n_bwd_blocks)
         spec_body<BwdTopo<NS>, NS, SPT, RING>(smem_raw, blockIdx.x, scores, bwd, T, N, stay, tables, status);
     else
-        spec_body<FwdTopo<NS>, NS, SPT, RING>(smem_raw, blockIdx.x - N, scores, fwd, T, N, stay, tables, status);
+        spec_body<FwdTopo<NS>, NS, SPT, RING>(smem_raw, blockIdx.x - n_bwd_blocks, scores, fwd, T, N, stay, tables, status);
 }
 
 template <int NS, int SPT, int CPB, int RING>
@@ -502,8 +511,9 @@ cudaError_t launch(const __half *scores, float *bwd, float *fwd, int T, int N, f
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
     if (e != cudaSuccess) return e;
     const int nblk = (N + CPB - 1) / CPB;
-    kern<<<fwd ? 2 * nblk : nblk, (NS / SPT) * CPB + 32, bytes, stream>>>(scores, bwd, fwd, T, N, nblk, stay,
-                                                                         tables, status);
+    const int n_bwd = bwd ? nblk : 0, n_fwd = fwd ? nblk : 0;
+    kern<<<n_bwd + n_fwd, (NS / SPT) * CPB + 32, bytes, stream>>>(scores, bwd, fwd, T, N, n_bwd, stay, tables,
+                                                                 status);
     return cudaGetLastError();
 }
 
@@ -515,7 +525,8 @@ cudaError_t launch_spec(const __half *scores, float *bwd, float *fwd, int T, int
     auto kern = scan_spec_kernel<NS, SPT, RING>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
     if (e != cudaSuccess) return e;
-    kern<<<fwd ? 2 * N : N, NS / SPT + 64, bytes, stream>>>(scores, bwd, fwd, T, N, stay, tables, status);
+    const int n_bwd = bwd ? N : 0, n_fwd = fwd ? N : 0;
+    kern<<<n_bwd + n_fwd, NS / SPT + 64, bytes, stream>>>(scores, bwd, fwd, T, N, n_bwd, stay, tables, status);
     return cudaGetLastError();
 }
 
@@ -527,7 +538,7 @@ cudaError_t of_launch_scans(const void *scores_fp16, float *bwd, float *fwd, int
     const __half *s = static_cast<const __half *>(scores_fp16);
     switch (state_len) {
         case 3: return launch<64, 1, 2, 8>(s, bwd, fwd, T, N, stay, tables, status, stream);
-        case 4: return launch_spec<256, 4, 8>(s, bwd, fwd, T, N, stay, tables, status, stream);
+        case 4: return launch_spec<256, 4, 6>(s, bwd, fwd, T, N, stay, tables, status, stream);
         case 5: return launch<1024, 2, 1, 6>(s, bwd, fwd, T, N, stay, tables, status, stream);
         default: return cudaErrorInvalidValue;
     }
