@@ -121,6 +121,38 @@ class ClockSampler(threading.Thread):
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+def measure_rotary(of, dev):
+    """openfish_rotary_emb_gpu on fp16 [32][1666][3][8][64] (Q and K heads in one call): device time
+    by CUDA events on the legacy default stream the call runs on, rotating over four tensors
+    (655 MB) so that no call finds its input in the 126 MB L2."""
+    import numpy as np
+    import torch
+    B, S, H, D = 32, 1666, 8, 64
+    half = D // 2
+    pos = np.arange(S)[:, None] * (10000.0 ** (-np.arange(half) / half))[None, :]
+    sin = torch.from_numpy(np.sin(pos).astype(np.float32)).to(dev)
+    cos = torch.from_numpy(np.cos(pos).astype(np.float32)).to(dev)
+    g = torch.Generator(device=dev).manual_seed(4)
+    xs = [torch.randn((B, S, 3, H, D), generator=g, device=dev, dtype=torch.float32).half() for _ in range(4)]
+    args = (B, S, 2 * H, D, half, S * 3 * H * D, 3 * H * D, D)
+    for x in xs:
+        of.rotary_emb_gpu(x, sin, cos, *args)
+    reps, total = 20, 0.0
+    for i in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        of.rotary_emb_gpu(xs[i % 4], sin, cos, *args)
+        e1.record()
+        e1.synchronize()
+        total += e0.elapsed_time(e1)
+    ms = total / reps
+    nbytes = 2 * B * S * 2 * H * D * 2 + 2 * S * half * 4
+    peak, _ = measured_peak()
+    return {"shape": "fp16 [32][1666][3][8][64], nheads=16", "ms": ms, "algorithmic_bytes": nbytes,
+            "achieved_gbs": nbytes / (ms * 1e-3) / 1e9, "frac_of_measured_hbm": nbytes / (ms * 1e-3) / 1e9 / peak,
+            "calls": reps}
+
+
 def physical_gpu_index(local_rank):
     vis = os.environ.get("CUDA_VISIBLE_DEVICES")
     if vis:
@@ -261,6 +293,16 @@ def main():
     clocks = sampler.finish()
     e2e_value = total_chunks * e2e_steps / e2e_s
 
+    # ---- wall time of openfish_decode_gpu itself, scores resident (what the reference's driver
+    # times, src/main.c:271-303), and the rotary helper on the encoder's packed QKV shape ------
+    api_wall = []
+    for _ in range(10):
+        torch.cuda.synchronize()
+        a0 = time.perf_counter()
+        of.decode_gpu(scores, STATE_LEN, gpubuf=gb)
+        api_wall.append(1e3 * (time.perf_counter() - a0))
+    rotary = measure_rotary(of, dev) if rank == 0 else None
+
     if rank == 0:
         peak, peak_src = measured_peak()
         per = {k: v / args.steps for k, v in ms.items()}
@@ -294,7 +336,10 @@ def main():
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(scores.numel() * 2),
                     "d2h_bytes_per_step": int(3 * n_local * T), "steps": e2e_steps,
                     "call": "openfish_decode_gpu after a page-locked host-to-device copy of the scores"},
-            "gpu_launches": of.lib().openfish_b200_kernels_per_decode() * args.steps,
+            "gpu_launches": of.lib().openfish_b200_kernels_per_decode() * args.steps * world,
+            "decode_gpu_wall_ms": {"best": min(api_wall), "median": statistics.median(api_wall), "calls": 10,
+                                   "note": "openfish_decode_gpu, scores resident, results malloc'ed on the host"},
+            "rotary": rotary,
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline:

@@ -103,6 +103,19 @@ int openfish_b200_decode_static(int T, int N, int C, const void *scores_TNC, int
                                 const openfish_opt_t *options, uint8_t *moves_gpu,
                                 char *sequence_gpu, char *qstring_gpu);
 
+/* The four helpers the reference's test driver (src/main.c:207-252,337-351) calls next to the
+ * public API; the reference declares them in an internal header (src/decode_cuda.h:35-55).
+ * Same names, arguments and behaviour, so that a driver written against the reference links
+ * against this library: select the calling thread's device; copy T*N*C fp16 scores from the
+ * host into a new device buffer / release it; write the gpubuf's bwd_NTC, post_NTC, qual_data,
+ * base_probs and total_probs as raw little-endian blobs of those names into the current
+ * directory (src/decode_cuda.cu:242-343).  Errors follow the library's error mode. */
+void set_device_cuda(int device);
+void *upload_scores_to_cuda(const int T, const int N, const int C, const void *scores_TNC);
+void free_scores_cuda(void *scores_TNC_gpu);
+void write_gpubuf_cuda(const uint64_t T, const uint64_t N, const int state_len,
+                       const openfish_gpubuf_t *gpubuf);
+
 #ifdef __cplusplus
 }
 #endif

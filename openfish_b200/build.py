@@ -1,4 +1,5 @@
-"""Builds libopenfish.so (C host layer + sm_100a kernels) in-tree with nvcc and gcc.
+"""Builds libopenfish.so (C host layer + sm_100a kernels) and the `openfish` command-line driver
+in-tree with nvcc and gcc.
 
     python -m openfish_b200.build            # build if sources are newer than the library
     python -m openfish_b200.build --force
@@ -12,6 +13,8 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libopenfish.so")
+CLI_SRC = os.path.join(HERE, "cli", "openfish_cli.c")
+CLI = os.path.join(HERE, "bin", "openfish")  # the command-line driver, linked against LIB
 CU = ["scan.cu", "beam_search.cu", "posterior_seq.cu", "rotary.cu", "decode_b200.cu", "decode_static.cu"]
 CC = ["openfish_api.c"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
@@ -20,10 +23,10 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
 
 
 def _stale():
-    if not os.path.exists(LIB):
+    if not os.path.exists(LIB) or not os.path.exists(CLI):
         return True
-    t = os.path.getmtime(LIB)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)]
+    t = min(os.path.getmtime(LIB), os.path.getmtime(CLI))
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [CLI_SRC]
     deps += [os.path.join(dp, f) for dp, _, fs in os.walk(os.path.join(ROOT, "include")) for f in fs]
     return any(os.path.getmtime(d) > t for d in deps)
 
@@ -52,6 +55,9 @@ def build(force=False, verbose=False):
             raise RuntimeError("build step failed: " + " ".join(cmd))
     link = [NVCC, "-shared", "-o", LIB] + objs + ["-cudart", "static", "-lm"]
     subprocess.run(link, check=True)
+    os.makedirs(os.path.dirname(CLI), exist_ok=True)
+    subprocess.run(["gcc", "-O2", "-Wall", "-std=gnu11", "-I", os.path.join(ROOT, "include"), CLI_SRC, "-o", CLI,
+                    "-L", LIB_DIR, "-lopenfish", "-Wl,-rpath,$ORIGIN/../lib", "-lm"], check=True)
     return LIB
 
 

@@ -31,6 +31,12 @@ int ofb_rotary(void *x, const void *sin_t, const void *cos_t, int batch, int seq
                int rotary_half, long long stride_batch, long long stride_seq,
                long long stride_head);
 
+/* Device selection and plain copies for driver programs (no CUDA headers needed on their side). */
+int ofb_set_device(int device);
+int ofb_device_upload(const void *host, size_t bytes, void **out);
+int ofb_device_free(void *device);
+int ofb_device_download(void *host, const void *device, size_t bytes);
+
 const char *ofb_error_text(void);
 
 #ifdef __cplusplus

@@ -306,3 +306,29 @@ extern "C" int ofb_rotary(void *x, const void *sin_t, const void *cos_t, int bat
     CU(cudaStreamSynchronize(0));
     return OPENFISH_B200_OK;
 }
+
+// ---- helpers for a driver program in the style of the reference's (src/decode_cuda.cu:214-240)
+extern "C" int ofb_set_device(int device) {
+    CU(cudaSetDevice(device));
+    return OPENFISH_B200_OK;
+}
+extern "C" int ofb_device_upload(const void *host, size_t bytes, void **out) {
+    void *d = nullptr;
+    CU(cudaMalloc(&d, bytes ? bytes : 1));
+    cudaError_t e = cudaMemcpy(d, host, bytes, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        cudaFree(d);
+        return fail(OPENFISH_B200_ERR_CUDA, "host-to-device copy failed: %s", cudaGetErrorString(e));
+    }
+    *out = d;
+    return OPENFISH_B200_OK;
+}
+extern "C" int ofb_device_free(void *device) {
+    CU(cudaFree(device));
+    return OPENFISH_B200_OK;
+}
+extern "C" int ofb_device_download(void *host, const void *device, size_t bytes) {
+    CU(cudaMemcpy(host, device, bytes, cudaMemcpyDeviceToHost));
+    return OPENFISH_B200_OK;
+}
+

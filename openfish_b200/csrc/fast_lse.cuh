@@ -39,25 +39,33 @@ __device__ __forceinline__ float lg2_approx(float x) {
     return y;
 }
 
+// ln of s in [1, 8): the power of two is split off so that lg2 works on [1,2), where its error is
+// absolute.  The exponent becomes a float through the 2^23 trick (an integer add and a float
+// subtraction) rather than a conversion instruction.
+__device__ __forceinline__ float ln_1to8(float s) {
+    const float kLn2 = 0.6931471805599453f;
+    const unsigned bits = __float_as_uint(s);
+    const float q = __uint_as_float(0x4b000000u | (bits >> 23)) - 8388735.0f;  // (2^23 + e) - (2^23 + 127)
+    const float f = __uint_as_float((bits & 0x007fffffu) | 0x3f800000u);
+    return (q + lg2_approx(f)) * kLn2;
+}
+
 // v: the five terms.  On success writes the reference-exact float to `out`.
 __device__ __forceinline__ bool lse5_try_fast(const float v[5], float &out) {
-    const float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
+    const float kLog2e = 1.4426950408889634f;
     const float m = fmaxf(fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3])), v[4]);
     float s = ex2_approx((v[0] - m) * kLog2e);
     s += ex2_approx((v[1] - m) * kLog2e);
     s += ex2_approx((v[2] - m) * kLog2e);
     s += ex2_approx((v[3] - m) * kLog2e);
     s += ex2_approx((v[4] - m) * kLog2e);
-    // s in [1, 5]: split off the power of two so lg2 works on [1,2), where its error is absolute
-    const unsigned bits = __float_as_uint(s);
-    const float q = (float)((int)(bits >> 23) - 127);
-    const float f = __uint_as_float((bits & 0x007fffffu) | 0x3f800000u);
-    const float l = (q + lg2_approx(f)) * kLn2;
+    const float l = ln_1to8(s);
     const float lo = m + (l - kLseEps);
     const float hi = m + (l + kLseEps);
     out = lo;
-    // NaN or infinite inputs compare unequal or are caught by the finiteness test
-    return lo == hi && fabsf(lo) < 3.0e38f;
+    // A NaN or infinite term makes the sum NaN (an infinite maximum gives inf - inf in its own
+    // term); ln_1to8 works on the bits and would not pass that on, so the sum is tested itself.
+    return lo == hi && s < 8.f;
 }
 
 }  // namespace ofd
@@ -71,7 +79,7 @@ namespace ofd {
 // confirmed or corrected by the value-exact routine.
 template <int K>
 __device__ __forceinline__ void lse5_fast_guess(const float (*v)[5], float *out, bool *ok) {
-    const float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
+    const float kLog2e = 1.4426950408889634f;
     float m[K], e[K][5], s[K], l[K];
 #pragma unroll
     for (int k = 0; k < K; ++k)
@@ -81,20 +89,17 @@ __device__ __forceinline__ void lse5_fast_guess(const float (*v)[5], float *out,
 #pragma unroll
         for (int k = 0; k < K; ++k) e[k][i] = ex2_approx((v[k][i] - m[k]) * kLog2e);
 #pragma unroll
-    for (int k = 0; k < K; ++k) s[k] = (((e[k][0] + e[k][1]) + e[k][2]) + e[k][3]) + e[k][4];
+    for (int k = 0; k < K; ++k) s[k] = ((e[k][0] + e[k][1]) + (e[k][2] + e[k][3])) + e[k][4];
 #pragma unroll
     for (int k = 0; k < K; ++k) {
-        const unsigned bits = __float_as_uint(s[k]);
-        const float q = (float)((int)(bits >> 23) - 127);
-        const float f = __uint_as_float((bits & 0x007fffffu) | 0x3f800000u);
-        l[k] = (q + lg2_approx(f)) * kLn2;
+        l[k] = ln_1to8(s[k]);
     }
 #pragma unroll
     for (int k = 0; k < K; ++k) {
         const float lo = m[k] + (l[k] - kLseEps);
         const float hi = m[k] + (l[k] + kLseEps);
         out[k] = m[k] + l[k];
-        ok[k] = lo == hi && fabsf(lo) < 3.0e38f;
+        ok[k] = lo == hi && s[k] < 8.f;  // (the second test fails for a NaN sum)
     }
 }
 
@@ -107,7 +112,7 @@ __device__ __forceinline__ void lse5_batch(const float (*v)[5], float *out, cons
     bool ok[K];
     // all K fast evaluations stage by stage, so that their instruction streams interleave
     {
-        const float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
+        const float kLog2e = 1.4426950408889634f;
         float m[K], e[K][5], s[K], l[K];
 #pragma unroll
         for (int k = 0; k < K; ++k)
@@ -128,17 +133,14 @@ __device__ __forceinline__ void lse5_batch(const float (*v)[5], float *out, cons
             for (int k = 0; k < K; ++k) s[k] += e[k][i];
 #pragma unroll
         for (int k = 0; k < K; ++k) {
-            const unsigned bits = __float_as_uint(s[k]);
-            const float q = (float)((int)(bits >> 23) - 127);
-            const float f = __uint_as_float((bits & 0x007fffffu) | 0x3f800000u);
-            l[k] = (q + lg2_approx(f)) * kLn2;
+            l[k] = ln_1to8(s[k]);
         }
 #pragma unroll
         for (int k = 0; k < K; ++k) {
             const float lo = m[k] + (l[k] - kLseEps);
             const float hi = m[k] + (l[k] + kLseEps);
             out[k] = lo;
-            ok[k] = lo == hi && fabsf(lo) < 3.0e38f;
+            ok[k] = lo == hi && s[k] < 8.f;  // (the second test fails for a NaN sum)
         }
     }
     int nbad = 0;

@@ -238,3 +238,81 @@ void openfish_rotary_emb_cpu(void *x, void *sin_buf, void *cos_buf, int batch_si
     clear_error();
     raise_error(__func__, OPENFISH_B200_ERR_NO_CPU_PATH, "this library has no CPU rotary path");
 }
+
+/* ---- what the reference's test driver calls besides the public API (src/decode_cuda.h:35-55,
+ * src/decode_cuda.cu:214-343): device selection, score upload, and a dump of the gpubuf's
+ * tensors into the current directory. */
+void set_device_cuda(int device) {
+    clear_error();
+    backend_failed(__func__, ofb_set_device(device));
+}
+
+void *upload_scores_to_cuda(const int T, const int N, const int C, const void *scores_TNC) {
+    clear_error();
+    if (!scores_TNC || T < 0 || N < 0 || C < 0) {
+        raise_error(__func__, OPENFISH_B200_ERR_ARGUMENT, "scores_TNC must not be NULL, extents not negative");
+        return NULL;
+    }
+    void *d = NULL;
+    if (backend_failed(__func__, ofb_device_upload(scores_TNC, (size_t)T * N * C * 2u, &d))) return NULL;
+    return d;
+}
+
+void free_scores_cuda(void *scores_TNC_gpu) {
+    clear_error();
+    backend_failed(__func__, ofb_device_free(scores_TNC_gpu));
+}
+
+/* One device tensor to a file, through a bounce buffer (the tensors reach gigabytes). */
+static int dump_tensor(const char *func, const char *path, const void *device, size_t bytes, void *bounce,
+                       size_t bounce_bytes) {
+    FILE *fp = fopen(path, "w");
+    if (!fp) {
+        char msg[300];
+        snprintf(msg, sizeof(msg), "cannot open %s for writing", path);
+        raise_error(func, OPENFISH_B200_ERR_ARGUMENT, msg);
+        return 1;
+    }
+    for (size_t off = 0; off < bytes; off += bounce_bytes) {
+        const size_t n = bytes - off < bounce_bytes ? bytes - off : bounce_bytes;
+        if (backend_failed(func, ofb_device_download(bounce, (const char *)device + off, n))) {
+            fclose(fp);
+            return 1;
+        }
+        if (fwrite(bounce, 1, n, fp) != n) {
+            char msg[300];
+            snprintf(msg, sizeof(msg), "short write to %s", path);
+            fclose(fp);
+            raise_error(func, OPENFISH_B200_ERR_ARGUMENT, msg);
+            return 1;
+        }
+    }
+    fclose(fp);
+    return 0;
+}
+
+void write_gpubuf_cuda(const uint64_t T, const uint64_t N, const int state_len, const openfish_gpubuf_t *gpubuf) {
+    clear_error();
+    if (!gpubuf || state_len < 3 || state_len > 5) {
+        raise_error(__func__, OPENFISH_B200_ERR_ARGUMENT, "gpubuf must not be NULL, state_len 3..5");
+        return;
+    }
+    if (backend_failed(__func__, ofb_gpubuf_check(gpubuf, (int)T, (int)N, state_len))) return;
+    const size_t ns = (size_t)states_of(state_len), bounce_bytes = (size_t)32 << 20;
+    void *bounce = malloc(bounce_bytes);
+    if (!bounce) {
+        raise_error(__func__, OPENFISH_B200_ERR_ALLOC, "out of host memory");
+        return;
+    }
+    const struct { const char *path; const void *dev; size_t bytes; } out[] = {
+        {"bwd_NTC.blob", gpubuf->bwd_NTC, N * (T + 1) * ns * sizeof(float)},
+        {"post_NTC.blob", gpubuf->post_NTC, N * (T + 1) * ns * sizeof(float)},
+        {"qual_data.blob", gpubuf->qual_data, N * T * 4 * sizeof(float)},
+        {"base_probs.blob", gpubuf->base_probs, N * T * sizeof(float)},
+        {"total_probs.blob", gpubuf->total_probs, N * T * sizeof(float)},
+    };
+    for (size_t i = 0; i < sizeof(out) / sizeof(out[0]); ++i)
+        if (dump_tensor(__func__, out[i].path, out[i].dev, out[i].bytes, bounce, bounce_bytes)) break;
+    free(bounce);
+}
+
