@@ -70,6 +70,10 @@ void openfish_b200_last_decode_ms(const openfish_gpubuf_t *gpubuf, float ms[4]);
  * posterior + traceback + sequence kernel, ms[7] unused (0). */
 void openfish_b200_last_decode_detail_ms(const openfish_gpubuf_t *gpubuf, float ms[8]);
 
+/* Device time, in milliseconds, of the calling thread's last openfish_rotary_emb_gpu call (CUDA
+ * events on the legacy default stream around the kernel). */
+float openfish_b200_last_rotary_ms(void);
+
 /* Number of kernels one decode call launches (for benchmark bookkeeping). */
 int openfish_b200_kernels_per_decode(void);
 

@@ -86,6 +86,7 @@ def lib():
         L.openfish_b200_error_text.restype = C.c_char_p
         L.openfish_b200_set_error_mode.argtypes = [i]
         L.openfish_b200_kernels_per_decode.restype = i
+        L.openfish_b200_last_rotary_ms.restype = C.c_float
         L.openfish_b200_decode_static.restype = i
         L.openfish_b200_decode_static.argtypes = [i, i, i, vp, i, C.POINTER(Opt), vp, vp, vp]
         L.get_openfish_log_level.restype = i
@@ -217,6 +218,11 @@ def rotary_emb_gpu(x_gpu, sin_gpu, cos_gpu, batch_size, seqlen, nheads, head_dim
                                   batch_size, seqlen, nheads, head_dim, rotary_half, stride_batch,
                                   stride_seq, stride_head)
     _check()
+
+
+def last_rotary_ms():
+    """Device time of this thread's last rotary_emb_gpu call."""
+    return float(lib().openfish_b200_last_rotary_ms())
 
 
 from .sharding import shard_range  # noqa: E402,F401

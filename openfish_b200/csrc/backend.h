@@ -31,6 +31,9 @@ int ofb_rotary(void *x, const void *sin_t, const void *cos_t, int batch, int seq
                int rotary_half, long long stride_batch, long long stride_seq,
                long long stride_head);
 
+/* Device time of the calling thread's last ofb_rotary call, in milliseconds. */
+float ofb_last_rotary_ms(void);
+
 /* Device selection and plain copies for driver programs (no CUDA headers needed on their side). */
 int ofb_set_device(int device);
 int ofb_device_upload(const void *host, size_t bytes, void **out);

@@ -293,19 +293,42 @@ extern "C" int ofb_last_decode_ms(const openfish_gpubuf_t *gpubuf, float ms[8]) 
     return OPENFISH_B200_OK;
 }
 
+// Device time of this thread's last rotary call: two events per device, made on first use.
+namespace {
+constexpr int kMaxDevices = 64;
+struct RotaryClock {
+    cudaEvent_t ev[kMaxDevices][2] = {};
+    bool made[kMaxDevices] = {};
+    float last_ms = 0.f;
+};
+thread_local RotaryClock t_rotary;
+}  // namespace
+
 extern "C" int ofb_rotary(void *x, const void *sin_t, const void *cos_t, int batch, int seqlen,
                           int nheads, int rotary_half, long long stride_batch,
                           long long stride_seq, long long stride_head) {
     int dev = 0, sms = 0;
     CU(cudaGetDevice(&dev));
     CU(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const bool timed = dev >= 0 && dev < kMaxDevices;
+    if (timed && !t_rotary.made[dev]) {
+        CU(cudaEventCreate(&t_rotary.ev[dev][0]));
+        CU(cudaEventCreate(&t_rotary.ev[dev][1]));
+        t_rotary.made[dev] = true;
+    }
     // the reference launches on the legacy default stream and waits for the device
     // (src/nn_cuda.cu:27-39); same stream here, and a wait on that stream only
+    if (timed) CU(cudaEventRecord(t_rotary.ev[dev][0], 0));
     CU(of_launch_rotary(x, sin_t, cos_t, batch, seqlen, nheads, rotary_half, stride_batch,
                         stride_seq, stride_head, sms, 0));
+    if (timed) CU(cudaEventRecord(t_rotary.ev[dev][1], 0));
     CU(cudaStreamSynchronize(0));
+    t_rotary.last_ms = 0.f;
+    if (timed) CU(cudaEventElapsedTime(&t_rotary.last_ms, t_rotary.ev[dev][0], t_rotary.ev[dev][1]));
     return OPENFISH_B200_OK;
 }
+
+extern "C" float ofb_last_rotary_ms(void) { return t_rotary.last_ms; }
 
 // ---- helpers for a driver program in the style of the reference's (src/decode_cuda.cu:214-240)
 extern "C" int ofb_set_device(int device) {

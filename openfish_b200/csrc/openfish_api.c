@@ -218,6 +218,8 @@ void openfish_rotary_emb_gpu(void *x_gpu, void *sin_gpu, void *cos_gpu, int batc
                                         rotary_half, stride_batch, stride_seq, stride_head));
 }
 
+float openfish_b200_last_rotary_ms(void) { return ofb_last_rotary_ms(); }
+
 void openfish_decode_cpu(const int T, const int N, const int C, int nthreads, void *scores_TNC,
                          const int state_len, const openfish_opt_t *options, uint8_t **moves,
                          char **sequence, char **qstring) {
