@@ -9,7 +9,8 @@ namespace ofx { struct Tables; }
 struct OfDecodeArgs {
     const __half *scores;      // [T][N][C] fp16, 16-byte aligned, C % 8 == 0, C >= 4*ns
     const float *bwd;          // [N][T+1][ns], from the backward scan
-    const float *fwd;          // [N][T+1][ns], from the forward scan (posterior kernel only)
+    const float *fwd;          // [N][T+1][ns], from the forward scan (posterior kernel only); null when
+                               // the forward scan has already written the posterior into `post`
     float *post;               // [N][T+1][ns] out
     unsigned char *bp;         // [N][T+1][32] packed back-pointers: beam search -> traceback
     int *init_kmers;           // [N][32] k-mers of the initial beam: beam search -> traceback

@@ -133,7 +133,8 @@ extern "C" int ofb_gpubuf_create(int T, int N, int state_len, openfish_gpubuf_t 
         // result arrays share one allocation so that one copy brings them back
         CU(cudaMalloc(&g->pub.bwd_NTC, tens));
         CU(cudaMalloc(&g->pub.post_NTC, tens));
-        CU(cudaMalloc(&g->d_fwd, tens));
+        // (models whose forward scan writes the posterior itself need no forward tensor)
+        if (!of_forward_posterior_fused(state_len)) CU(cudaMalloc(&g->d_fwd, tens));
         CU(cudaMalloc(&g->d_results, 3 * nt));
         g->pub.moves = g->d_results;
         g->pub.sequence = reinterpret_cast<char *>(g->d_results + nt);
@@ -221,14 +222,19 @@ extern "C" int ofb_decode_submit(int T, int N, int C, const void *scores, int st
 
     // stream:  backward scan -> beam search ----------------------> posterior + sequence -> copies
     // stream2:                  forward scan (beside the beam search) --^
+    // (for hac the forward scan kernel also writes the posterior, and a.fwd is null)
     CU(cudaEventRecord(g->ev[0], g->stream));
     CU(of_launch_scans(scores, g->pub.bwd_NTC, nullptr, T, N, state_len, blank_score, g->d_tables,
                        g->d_status, g->stream));
     CU(cudaEventRecord(g->ev[1], g->stream));
     CU(cudaStreamWaitEvent(g->stream2, g->ev[1], 0));
     CU(cudaEventRecord(g->ev[5], g->stream2));
-    CU(of_launch_scans(scores, nullptr, g->d_fwd, T, N, state_len, blank_score, g->d_tables,
-                       g->d_status, g->stream2));
+    if (of_forward_posterior_fused(state_len))
+        CU(of_launch_forward_posterior(scores, g->pub.bwd_NTC, g->pub.post_NTC, T, N, state_len, blank_score,
+                                       g->d_tables, g->d_status, g->stream2));
+    else
+        CU(of_launch_scans(scores, nullptr, g->d_fwd, T, N, state_len, blank_score, g->d_tables,
+                           g->d_status, g->stream2));
     CU(cudaEventRecord(g->ev[6], g->stream2));
     CU(of_launch_beam_search(a, g->stream));
     CU(cudaEventRecord(g->ev[2], g->stream));

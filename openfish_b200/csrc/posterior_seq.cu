@@ -6,7 +6,8 @@
 // compute_qual_data (:530-605) and generate_sequence (:52-121); semantics are those of the CPU
 // routines (src/decode_cpu.c:115,121-147; src/beam_search.c:430-496 and 49-99).
 //
-// First the posterior = softmax over states of fwd + bwd: rows are independent, so each warp
+// First (unless the forward scan kernel has done it already: a.fwd null) the posterior =
+// softmax over states of fwd + bwd: rows are independent, so each warp
 // takes rows of its own and streams them straight from and to HBM (this part is bound by HBM
 // bandwidth: it reads 2(T+1)ns and writes (T+1)ns floats per chunk).  No per-row maximum is
 // needed: the log partition function is the same for every row, so one offset taken from row 0
@@ -84,7 +85,7 @@ posterior_seq_kernel(const OfDecodeArgs a) {
     // 16 bytes for the 64-state model), one shuffle reduction for the row sum.  The softmax
     // offset is the maximum of fwd+bwd at row 0 (= bwd row 0, fwd is zero there): the log
     // partition function is the same for every row, so every exponent stays in range.
-    if (warp == 0) {
+    if (a.fwd != nullptr && warp == 0) {
         float m = -FLT_MAX;
         for (int s = lane; s < NS; s += 32) m = fmaxf(m, bwd_chunk[s]);
         m = ofd::warp_max(m);
@@ -95,7 +96,7 @@ posterior_seq_kernel(const OfDecodeArgs a) {
     constexpr int PER = NS / 32;              // states per lane: 2, 8 or 32
     constexpr int VEC = PER >= 4 ? 4 : PER;   // floats per access
     constexpr int NV = PER / VEC;
-    for (int t = warp; t <= T; t += NWARP) {
+    for (int t = warp; t <= T && a.fwd != nullptr; t += NWARP) {
         const float *fr = fwd_chunk + (size_t)t * NS, *br = bwd_chunk + (size_t)t * NS;
         float e[PER];
         float part = 0.f;

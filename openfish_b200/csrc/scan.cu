@@ -296,14 +296,23 @@ struct SpecSmem {
     int abort_flag;
 };
 
-template <class Topo, int NS, int SPT, int RING>
+//
+// POST (forward direction only): the rows are not written out; a fourth kind of warp turns each
+// row, once it is final, into the posterior row  softmax_s(fwd[t][s] + bwd[t][s])  and writes
+// that (`out` is then the posterior tensor and `bwd_in` the finished backward scores).  Row r is
+// final after the barrier that ends timestep r (its guesses have been checked by then) and its
+// buffer is written again during timestep r+2, so the posterior warp takes it during timestep
+// r+1; the last two rows are taken after the scan.  The arithmetic is that of the stand-alone
+// posterior loop in posterior_seq.cu, operation for operation.
+template <class Topo, int NS, int SPT, int RING, bool POST>
 __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, const __half *scores,
-                                          float *out, int T, int N, float stay,
+                                          float *out, const float *bwd_in, int T, int N, float stay,
                                           const ofx::Tables *tables, int *status) {
     constexpr int NJ = NS / 4;
     constexpr int TPC = NS / SPT;
     using Smem = SpecSmem<NS, SPT, RING>;
     constexpr int NW = Smem::NW, PER = Smem::kPerWarp;
+    static_assert(!POST || Topo::kForward, "the posterior rides on the forward scan");
     static_assert(TPC % 32 == 0, "scan warps must be full");
     Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
 
@@ -356,6 +365,71 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
                               Smem::kRowBytes, &sm.full[slot]);
             }
         }
+        if (POST) __syncthreads();  // the last row is final
+        return;
+    }
+
+    if (POST && warp == NW + 2) {
+        // ------------------------------------------------------------------ posterior warp
+        constexpr int PERL = NS / 32;  // states per lane, as two or more 16-byte pieces
+        constexpr int NV = PERL / 4;
+        static_assert(PERL % 4 == 0, "16-byte accesses");
+        const float kLog2e = 1.4426950408889634f;
+        const float *bwd_chunk = bwd_in + (size_t)chunk * (size_t)(T + 1) * NS;
+        // the softmax offset: the maximum of fwd + bwd at row 0 (fwd is zero there); the log
+        // partition function is the same for every row, so every exponent stays in range
+        float m0 = -3.0e38f;
+        for (int st = lane; st < NS; st += 32) m0 = fmaxf(m0, bwd_chunk[st]);
+        m0 = ofd::warp_max(m0);
+        float4 b[NV];
+        auto fetch = [&](int r) {
+#pragma unroll
+            for (int q = 0; q < NV; ++q)
+                b[q] = *reinterpret_cast<const float4 *>(bwd_chunk + (size_t)r * NS + (q * 32 + lane) * 4);
+        };
+        auto emit = [&](int r) {  // b holds backward row r
+            const float *fr = sm.alpha[r % 3];
+            float e[PERL];
+            float part = 0.f;
+#pragma unroll
+            for (int q = 0; q < NV; ++q) {
+                const float4 f = *reinterpret_cast<const float4 *>(fr + (q * 32 + lane) * 4);
+                const float fv[4] = {f.x, f.y, f.z, f.w}, bv[4] = {b[q].x, b[q].y, b[q].z, b[q].w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    e[q * 4 + k] = ofd::ex2_approx(((fv[k] + bv[k]) - m0) * kLog2e);
+                    part += e[q * 4 + k];
+                }
+            }
+#pragma unroll
+            for (int o = 16; o; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+            const float inv = 1.0f / part;
+            float *pr = out_chunk + (size_t)r * NS;
+#pragma unroll
+            for (int q = 0; q < NV; ++q)
+                *reinterpret_cast<float4 *>(pr + (q * 32 + lane) * 4) =
+                    make_float4(e[q * 4] * inv, e[q * 4 + 1] * inv, e[q * 4 + 2] * inv, e[q * 4 + 3] * inv);
+        };
+        fetch(0);
+        __syncthreads();  // start of the scan
+        int next_row = 0;
+        for (int i = 0; i < T; ++i) {
+            // during timestep i the rows up to i-1 are final (and row 0 always is)
+            if (next_row == 0 || next_row <= i - 1) {
+                emit(next_row);
+                ++next_row;
+                fetch(next_row);  // next_row <= T
+            }
+            __syncthreads();
+            if (sm.n_wrong[i & 1]) __syncthreads();
+        }
+        while (next_row <= T - 1) {  // final since the last timestep's barrier
+            emit(next_row);
+            ++next_row;
+            fetch(next_row);
+        }
+        __syncthreads();  // the last row is final
+        emit(T);
         return;
     }
 
@@ -396,9 +470,14 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
                 __syncwarp();
             }
             if (i == T) {
-                // the last row: nobody reads it any more, just correct it
-                float *row = out_chunk + (size_t)Topo::out_row(T - 1, T) * NS;
-                for (int e = lane; e < nw; e += 32) row[sm.wrong_state[e]] = sm.wrong_value[e];
+                // the last row: no timestep reads it any more, just correct it
+                if (POST) {
+                    for (int e = lane; e < nw; e += 32) sm.alpha[T % 3][sm.wrong_state[e]] = sm.wrong_value[e];
+                    __syncthreads();  // the last row is final
+                } else {
+                    float *row = out_chunk + (size_t)Topo::out_row(T - 1, T) * NS;
+                    for (int e = lane; e < nw; e += 32) row[sm.wrong_state[e]] = sm.wrong_value[e];
+                }
                 break;
             }
             if (lane == 0) sm.n_wrong[i & 1] = nw;
@@ -408,7 +487,7 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
                 for (int e = lane; e < nw; e += 32) {
                     const int s = sm.wrong_state[e];
                     sm.alpha[i % 3][s] = sm.wrong_value[e];
-                    prev_row[s] = sm.wrong_value[e];
+                    if (!POST) prev_row[s] = sm.wrong_value[e];
                 }
                 __syncwarp();
                 // the five states of timestep i's row that read a corrected value
@@ -421,7 +500,7 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
                     float x;  // certified fp32 evaluation first: it settles all but about 1 in 100
                     if (!ofd::lse5_try_fast(v, x)) x = ofx::lse5_exact(v, tr);
                     sm.alpha[(i + 1) % 3][dep] = x;
-                    this_row[dep] = x;
+                    if (!POST) this_row[dep] = x;
                 }
                 __syncthreads();  // corrections in place
             }
@@ -432,8 +511,10 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
     // ---------------------------------------------------------------------- scan warps
     const int j = tid % NJ;
     const int k0 = (tid / NJ) * SPT;
+    if (!POST) {
 #pragma unroll
-    for (int k = 0; k < SPT; ++k) out_chunk[(size_t)Topo::zero_row(T) * NS + Topo::state(j, k0 + k)] = 0.f;
+        for (int k = 0; k < SPT; ++k) out_chunk[(size_t)Topo::zero_row(T) * NS + Topo::state(j, k0 + k)] = 0.f;
+    }
     __syncthreads();
     const uint32_t lt_mask = (1u << lane) - 1u;
     for (int i = 0; i < T; ++i) {
@@ -469,10 +550,11 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
             }
         }
         if (lane == 0) sm.n_listed[i & 1][warp] = total;
-        thread_store<Topo, SPT>(sm.alpha[(i + 1) % 3], out_chunk + (size_t)Topo::out_row(i, T) * NS, j, k0, res, true);
+        thread_store<Topo, SPT>(sm.alpha[(i + 1) % 3], out_chunk + (size_t)Topo::out_row(i, T) * NS, j, k0, res, !POST);
         __syncthreads();
         if (sm.n_wrong[i & 1]) __syncthreads();  // the checker is correcting this row's readers
     }
+    if (POST) __syncthreads();  // the last row is final
 }
 
 // ------------------------------------------------------------------------------------------
@@ -497,9 +579,21 @@ scan_spec_kernel(const __half *__restrict__ scores, float *__restrict__ bwd, flo
                  int *status) {
     extern __shared__ unsigned char smem_raw[];
     if ((int)blockIdx.x < n_bwd_blocks)
-        spec_body<BwdTopo<NS>, NS, SPT, RING>(smem_raw, blockIdx.x, scores, bwd, T, N, stay, tables, status);
+        spec_body<BwdTopo<NS>, NS, SPT, RING, false>(smem_raw, blockIdx.x, scores, bwd, nullptr, T, N, stay, tables,
+                                                     status);
     else
-        spec_body<FwdTopo<NS>, NS, SPT, RING>(smem_raw, blockIdx.x - n_bwd_blocks, scores, fwd, T, N, stay, tables, status);
+        spec_body<FwdTopo<NS>, NS, SPT, RING, false>(smem_raw, blockIdx.x - n_bwd_blocks, scores, fwd, nullptr, T, N,
+                                                     stay, tables, status);
+}
+
+// Forward scan with the posterior on top: one block per chunk, reads the finished backward scores.
+template <int NS, int SPT, int RING>
+__global__ void __launch_bounds__(NS / SPT + 96)
+scan_spec_posterior_kernel(const __half *__restrict__ scores, const float *__restrict__ bwd,
+                           float *__restrict__ post, int T, int N, float stay,
+                           const ofx::Tables *__restrict__ tables, int *status) {
+    extern __shared__ unsigned char smem_raw[];
+    spec_body<FwdTopo<NS>, NS, SPT, RING, true>(smem_raw, blockIdx.x, scores, post, bwd, T, N, stay, tables, status);
 }
 
 template <int NS, int SPT, int CPB, int RING>
@@ -530,7 +624,29 @@ cudaError_t launch_spec(const __half *scores, float *bwd, float *fwd, int T, int
     return cudaGetLastError();
 }
 
+template <int NS, int SPT, int RING>
+cudaError_t launch_spec_posterior(const __half *scores, const float *bwd, float *post, int T, int N, float stay,
+                                  const ofx::Tables *tables, int *status, cudaStream_t stream) {
+    using Smem = SpecSmem<NS, SPT, RING>;
+    const size_t bytes = sizeof(Smem) + 128;
+    auto kern = scan_spec_posterior_kernel<NS, SPT, RING>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) return e;
+    kern<<<N, NS / SPT + 96, bytes, stream>>>(scores, bwd, post, T, N, stay, tables, status);
+    return cudaGetLastError();
+}
+
 }  // namespace
+
+bool of_forward_posterior_fused(int state_len) { return state_len == 4; }
+
+cudaError_t of_launch_forward_posterior(const void *scores_fp16, const float *bwd, float *post, int T, int N,
+                                        int state_len, float stay, const ofx::Tables *tables, int *status,
+                                        cudaStream_t stream) {
+    if (state_len != 4 || T < 1) return cudaErrorInvalidValue;
+    return launch_spec_posterior<256, 4, 6>(static_cast<const __half *>(scores_fp16), bwd, post, T, N, stay, tables,
+                                            status, stream);
+}
 
 cudaError_t of_launch_scans(const void *scores_fp16, float *bwd, float *fwd, int T, int N,
                             int state_len, float stay, const ofx::Tables *tables, int *status,

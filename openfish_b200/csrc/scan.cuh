@@ -9,3 +9,11 @@ namespace ofx { struct Tables; }
 cudaError_t of_launch_scans(const void *scores_fp16, float *bwd, float *fwd, int T, int N,
                             int state_len, float stay, const ofx::Tables *tables, int *status,
                             cudaStream_t stream);
+
+// Forward scan and posterior in one kernel, for the models that have it (of_forward_posterior_fused):
+// reads the finished backward scores, writes post = softmax_s(fwd + bwd) [N][T+1][ns]; the forward
+// scores themselves never leave the chip.
+bool of_forward_posterior_fused(int state_len);
+cudaError_t of_launch_forward_posterior(const void *scores_fp16, const float *bwd, float *post, int T,
+                                        int N, int state_len, float stay, const ofx::Tables *tables,
+                                        int *status, cudaStream_t stream);
