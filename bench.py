@@ -42,10 +42,10 @@ CONFIG = {"workload": WORKLOAD,
 
 # algorithmic bytes per chunk (fp16 scores read once per scan; bwd written then read; post,
 # moves, sequence, qstring written)
-B_KERNEL = {"bwd_scan": T * 4 * NS * 2 + (T + 1) * NS * 4,          # scores in, bwd out
-            "fwd_scan": T * 4 * NS * 2 + (T + 1) * NS * 4,          # scores in, fwd out
+B_KERNEL = {"bwd_scan": T * 4 * NS * 2 + (T + 1) * NS * 4,              # scores in, bwd out
+            "fwd_scan": T * 4 * NS * 2 + 2 * (T + 1) * NS * 4,          # scores, bwd in; post out (forward scan + posterior)
             "beam_search": T * 4 * NS * 2 + (T + 1) * NS * 4 + 32 * (T + 1),  # scores, bwd in; back-pointers out
-            "posterior_seq": 3 * (T + 1) * NS * 4 + 32 * (T + 1) + 3 * T}     # fwd, bwd in; post, results out
+            "posterior_seq": 32 * (T + 1) + 9 * 4 * T + 3 * T}          # back-pointers, <= 9 posteriors per step in; results out
 B_CHUNK = 2 * T * 4 * NS * 2 + 3 * (T + 1) * NS * 4 + 3 * T
 
 
@@ -375,7 +375,7 @@ def main():
             "bases_per_sec": bases / dev_s * 1.0,
             "wall_ms_per_step": 1e3 * wall_s / args.steps,
             "kernel_ms": {k: per[k] for k in ("bwd_scan", "fwd_scan", "beam_search", "posterior_seq", "d2h")},
-            "kernel_overlap": "fwd_scan runs on a second stream beside beam_search; the others are sequential",
+            "kernel_overlap": "fwd_scan (forward scan + posterior) runs on a second stream beside beam_search; the others are sequential",
             "roofline": {"bound": "hbm", "kernel": dom, "launches_per_decode": len(launches),
                          "avg_launch_ms": dom_ms, "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": ncu_traffic(dom), "peak_source": peak_src,

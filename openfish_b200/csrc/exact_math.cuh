@@ -43,6 +43,12 @@ inline void fill_tables(Tables *t) {
         t->rcp_c[i] = 1.0 / c;
         t->log_c[i] = log(c);
     }
+    // The first interval is expanded about 1 itself: log(y) is then exact for y = 1 and carries
+    // a relative, not an absolute, error for y just above 1.  That matters because sums of the
+    // form 1 + k*2^-23 (one dominant term) put max + log(sum) within k^2 * 2^-47 of a rounding
+    // tie whenever the maximum is a round number, as it is on the first timestep.
+    t->rcp_c[0] = 1.0;
+    t->log_c[0] = 0.0;
 }
 
 OFX_HD double d_fma(double a, double b, double c) {
@@ -125,15 +131,18 @@ OFX_HD double exp_neg(double a, const double *tab, int stride = 1) {
     return make_double(hi_word(e) + ((uint32_t)(n & ~63) << 14), lo_word(e));
 }
 
-// log(y) for y in [1, 8).  y = c*(1+u) with c the centre of y's 1/64-binade interval;
-// log1p(u) by a degree-5 Taylor polynomial, |u| <= 2^-7.  6 FP64 operations.
+// log(y) for y in [1, 8).  y = c*(1+u) with c the centre of y's 1/64-binade interval (the
+// first interval's lower end, 1, instead of its centre); log1p(u) by a degree-7 Taylor
+// polynomial, |u| <= 2^-7 (first interval: 0 <= u < 2^-6, truncation < 2^-51).  8 FP64 operations.
 OFX_HD double log_1to8(double y, const double *rcp_c, const double *log_c) {
     // y outside [1,8) (only possible for non-finite or garbage inputs) is pinned to the table's
     // ends so the lookup can never leave it
     uint32_t i = (hi_word(y) >> 14) - (1023u << 6);
     i = i < (uint32_t)kLogTab ? i : (uint32_t)(kLogTab - 1);
     const double u = d_fma(y, rcp_c[i], -1.0);
-    double p = d_fma(u, 0.2, -0.25);
+    double p = d_fma(u, 1.0 / 7.0, -1.0 / 6.0);
+    p = d_fma(p, u, 0.2);
+    p = d_fma(p, u, -0.25);
     p = d_fma(p, u, 1.0 / 3.0);
     p = d_fma(p, u, -0.5);
     p = d_fma(p, u, 1.0);

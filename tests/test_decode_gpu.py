@@ -85,6 +85,22 @@ def test_degenerate_scores(native_lib, oracle_mod):
     check(native_lib, oracle_mod, s, 3, min_identical=1.0)
 
 
+@pytest.mark.parametrize("sl,scale,shift", [(4, 8.0, 0.0), (4, 1.0, -40.0), (3, 30.0, 0.0), (5, 0.25, 3.0)])
+def test_score_ranges_far_from_the_usual(native_lib, oracle_mod, sl, scale, shift):
+    # large scores (coarse float grid, everything certified), strongly negative ones (the running
+    # scores fall instead of rising), tiny ones (fine grid, the exact routine everywhere)
+    from openfish_b200 import synth
+    T, N = (500, 4) if sl < 5 else (200, 2)
+    s = (synth.make_scores(T, N, sl, 90 + sl).astype(np.float32) * scale + shift).astype(np.float16)
+    check(native_lib, oracle_mod, s, sl, min_identical=1.0)
+
+
+def test_long_chunks(native_lib, oracle_mod):
+    from openfish_b200 import synth
+    check(native_lib, oracle_mod, synth.make_scores(5000, 3, 4, 97), 4, min_identical=1.0)
+    check(native_lib, oracle_mod, synth.make_scores(6000, 5, 3, 98), 3, min_identical=1.0)
+
+
 @pytest.mark.parametrize("okw", [dict(beam_cut=0.0), dict(beam_cut=1.5), dict(beam_cut=1e6),
                                  dict(q_scale=0.95, q_shift=-0.2), dict(q_scale=3.0, q_shift=10.0)])
 def test_options(native_lib, oracle_mod, okw):

@@ -68,6 +68,29 @@ def test_backward_scan_bit_exact(host, oracle_mod, sl, T, N, seed, p_step):
     assert np.array_equal(out, ref)
 
 
+@pytest.mark.parametrize("sl,scale,shift,seed", [(4, 8.0, 0.0, 94), (3, 30.0, 0.0, 93), (3, 64.0, 0.0, 8),
+                                                 (4, 1.0, -40.0, 94), (3, 0.25, 3.0, 95)])
+def test_backward_scan_bit_exact_on_wide_score_ranges(host, oracle_mod, sl, scale, shift, seed):
+    # one dominant term makes the sum 1 + k*2^-23; with a round maximum (first timestep: the stay
+    # score itself) max + log(sum) then sits within k^2 * 2^-47 of a rounding tie, which only a log
+    # with a relative error near 1 decides correctly
+    from openfish_b200 import synth
+    T, N = 300, 4
+    sc = (synth.make_scores(T, N, sl, seed).astype(np.float32) * scale + shift).astype(np.float16).astype(np.float32)
+    ref = oracle_mod.backward_scan(sc, sl)
+    out = np.zeros_like(ref)
+    for c in range(N):
+        host.host_backward_scan(sc, out, c, T, N, 4 ** sl)
+    assert np.array_equal(out, ref)
+
+
+def test_log_is_relative_near_one(host):
+    for k in (0, 1, 2, 3, 7, 100, 12345):
+        y = 1.0 + k * 2.0 ** -23
+        want = float(np.log1p(np.float64(k) * 2.0 ** -23))
+        assert abs(host.host_log_1to8(y) - want) <= 2.0 ** -52 * max(want, 2.0 ** -30)
+
+
 def test_backward_scan_bit_exact_on_reference_golden(host, oracle_mod):
     from conftest import load_golden
     sc = load_golden("ref_fast_chunk")["scores"].astype(np.float32)
