@@ -95,6 +95,26 @@ def test_score_ranges_far_from_the_usual(native_lib, oracle_mod, sl, scale, shif
     check(native_lib, oracle_mod, s, sl, min_identical=1.0)
 
 
+def test_random_shapes_ranges_and_options(native_lib, oracle_mod):
+    # seeded differential runs over shapes, score scale/offset, stay-heavy paths, sparse scores
+    # and options; every case must meet the full gates with all chunks identical
+    from openfish_b200 import synth
+    rng = np.random.default_rng(20261)
+    for _ in range(60):
+        sl = int(rng.choice([3, 3, 4, 4, 4, 5]))
+        T = int(rng.integers(1, 900)) if sl < 5 else int(rng.integers(1, 200))
+        N = int(rng.integers(1, 7)) if sl < 5 else int(rng.integers(1, 3))
+        scale = float(rng.choice([0.05, 0.3, 1, 1, 2, 4, 8, 16, 40]))
+        shift = float(rng.choice([-12, -3, 0, 0, 0, 2, 6]))
+        okw = dict(beam_cut=float(rng.choice([100.0, 100.0, 3.0, 1e4, 1.01])), q_scale=float(rng.choice([1.0, 0.95])),
+                   q_shift=float(rng.choice([0.0, -0.2])))
+        s = synth.make_scores(T, N, sl, int(rng.integers(1, 1 << 30)), p_step=float(rng.choice([0.1, 0.5, 0.8, 1.0])))
+        s = (s.astype(np.float32) * scale + shift).astype(np.float16)
+        if rng.random() < 0.2:
+            s[rng.random(s.shape) < 0.35] = np.float16(-5.0 * min(scale, 4))
+        check(native_lib, oracle_mod, s, sl, okw, threads=8, min_identical=1.0)
+
+
 def test_long_chunks(native_lib, oracle_mod):
     from openfish_b200 import synth
     check(native_lib, oracle_mod, synth.make_scores(5000, 3, 4, 97), 4, min_identical=1.0)
