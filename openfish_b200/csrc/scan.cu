@@ -152,6 +152,70 @@ __device__ __forceinline__ void thread_store(float *smem_row, float *gmem_row, i
 }
 
 // ------------------------------------------------------------------------------------------
+// One row of the posterior, softmax_s(fwd[s] + bwd[s]), by one warp: the forward row comes from
+// shared memory, the backward row was fetched from HBM into registers a timestep earlier.  Lane l
+// takes the states (q*32 + l)*VEC .. +VEC-1; the arithmetic and its order are those of the
+// stand-alone posterior loop in posterior_seq.cu (softmax offset m0 = the maximum of row 0, where
+// fwd is zero: the log partition function is the same for every row, so exponents stay in range).
+template <int NS>
+struct PosteriorRow {
+    static constexpr int PERL = NS / 32;
+    static constexpr int VEC = PERL >= 4 ? 4 : PERL;
+    static constexpr int NV = PERL / VEC;
+    float b[PERL];
+
+    __device__ static float row_max(const float *row, int lane) {
+        float m = -3.0e38f;
+        for (int st = lane; st < NS; st += 32) m = fmaxf(m, row[st]);
+        return ofd::warp_max(m);
+    }
+    __device__ static void load(float *d, const float *p) {
+        if constexpr (VEC == 4) {
+            const float4 v = *reinterpret_cast<const float4 *>(p);
+            d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+        } else if constexpr (VEC == 2) {
+            const float2 v = *reinterpret_cast<const float2 *>(p);
+            d[0] = v.x; d[1] = v.y;
+        } else {
+            d[0] = *p;
+        }
+    }
+    __device__ void fetch(const float *bwd_row, int lane) {
+#pragma unroll
+        for (int q = 0; q < NV; ++q) load(b + q * VEC, bwd_row + (q * 32 + lane) * VEC);
+    }
+    // (the exponentials take the place of the backward row: fetch the next one afterwards)
+    __device__ void emit(const float *fwd_row, float *post_row, float m0, int lane) {
+        const float kLog2e = 1.4426950408889634f;
+        float part = 0.f;
+#pragma unroll
+        for (int q = 0; q < NV; ++q) {
+            float f[VEC];
+            load(f, fwd_row + (q * 32 + lane) * VEC);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) {
+                b[q * VEC + k] = ofd::ex2_approx(((f[k] + b[q * VEC + k]) - m0) * kLog2e);
+                part += b[q * VEC + k];
+            }
+        }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+        const float inv = 1.0f / part;
+#pragma unroll
+        for (int q = 0; q < NV; ++q) {
+            float *p = post_row + (q * 32 + lane) * VEC;
+            const float *e = b + q * VEC;
+            if constexpr (VEC == 4)
+                *reinterpret_cast<float4 *>(p) = make_float4(e[0] * inv, e[1] * inv, e[2] * inv, e[3] * inv);
+            else if constexpr (VEC == 2)
+                *reinterpret_cast<float2 *>(p) = make_float2(e[0] * inv, e[1] * inv);
+            else
+                *p = e[0] * inv;
+        }
+    }
+};
+
+// ------------------------------------------------------------------------------------------
 // Plain variant: CPB chunks per block; uncertified states are settled within the timestep.
 
 template <int NS, int CPB, int RING>
@@ -167,13 +231,19 @@ struct ScanSmem {
     int abort_flag;
 };
 
-template <class Topo, int NS, int SPT, int CPB, int RING>
+// POST (forward direction only): the rows are not written out; one more warp turns each row
+// into the posterior row and writes that (`out` is then the posterior tensor and `bwd_in` the
+// finished backward scores).  Row i is complete when timestep i starts and its buffer is written
+// again in timestep i+1, so the posterior warp takes it during timestep i, beside the scan warps
+// that read it too; the last row is taken after the scan.
+template <class Topo, int NS, int SPT, int CPB, int RING, bool POST>
 __device__ __forceinline__ void scan_body(unsigned char *smem_raw, int block, const __half *scores,
-                                          float *out, int T, int N, float stay,
+                                          float *out, const float *bwd_in, int T, int N, float stay,
                                           const ofx::Tables *tables, int *status) {
     constexpr int NJ = NS / 4;
     constexpr int TPC = NS / SPT;
     static_assert(TPC % 32 == 0, "a warp must not straddle two chunks");
+    static_assert(!POST || Topo::kForward, "the posterior rides on the forward scan");
     using Smem = ScanSmem<NS, CPB, RING>;
     Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
 
@@ -202,6 +272,33 @@ __device__ __forceinline__ void scan_body(unsigned char *smem_raw, int block, co
     // the scans address scores as [T][N][4ns] whatever C is (src/decode_cpu.c:16-18,27,59-62,80)
     const size_t t_stride = (size_t)N * NS * 4;
     const __half *blk_scores = scores + (size_t)chunk0 * NS * 4;
+
+    if (POST && tid >= TPC * CPB + 32) {
+        // ------------------------------------------------------------------ posterior warp
+        const int lane = tid & 31;
+        PosteriorRow<NS> pr[CPB];
+        float m0[CPB];
+        const float *bwd_blk = bwd_in + (size_t)chunk0 * (size_t)(T + 1) * NS;
+        float *post_blk = out + (size_t)chunk0 * (size_t)(T + 1) * NS;
+#pragma unroll
+        for (int c = 0; c < CPB; ++c)
+            if (c < nlive) {
+                m0[c] = PosteriorRow<NS>::row_max(bwd_blk + (size_t)c * (T + 1) * NS, lane);
+                pr[c].fetch(bwd_blk + (size_t)c * (T + 1) * NS, lane);
+            }
+        __syncthreads();  // start of the scan
+        for (int i = 0; i <= T; ++i) {
+#pragma unroll
+            for (int c = 0; c < CPB; ++c)
+                if (c < nlive) {
+                    const size_t row = ((size_t)c * (T + 1) + i) * NS;
+                    pr[c].emit(sm.alpha[i & 1][c], post_blk + row, m0[c], lane);
+                    if (i < T) pr[c].fetch(bwd_blk + row + NS, lane);
+                }
+            if (i < T) __syncthreads();  // end of timestep i
+        }
+        return;
+    }
 
     if (tid >= TPC * CPB) {
         // ------------------------------------------------------------------ copy warp
@@ -237,7 +334,7 @@ __device__ __forceinline__ void scan_body(unsigned char *smem_raw, int block, co
     const bool live = chunk < N;
     const ofx::TabRef tr = {sm.exp2_rep + (tid & (kExpCopies - 1)), kExpCopies, sm.rcp_c, sm.log_c};
     float *out_chunk = out + (size_t)(live ? chunk : 0) * (size_t)(T + 1) * NS;
-    if (live) {
+    if (live && !POST) {
 #pragma unroll
         for (int k = 0; k < SPT; ++k) out_chunk[(size_t)Topo::zero_row(T) * NS + Topo::state(j, k0 + k)] = 0.f;
     }
@@ -253,7 +350,7 @@ __device__ __forceinline__ void scan_body(unsigned char *smem_raw, int block, co
             ofd::lse5_batch<SPT>(v, res, tr);
         }
         thread_store<Topo, SPT>(sm.alpha[(i & 1) ^ 1][cl], out_chunk + (size_t)Topo::out_row(i, T) * NS, j, k0,
-                                res, live);
+                                res, live && !POST);
         __syncthreads();  // row complete; the copy warp has confirmed the next score row
     }
 }
@@ -371,45 +468,11 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
 
     if (POST && warp == NW + 2) {
         // ------------------------------------------------------------------ posterior warp
-        constexpr int PERL = NS / 32;  // states per lane, as two or more 16-byte pieces
-        constexpr int NV = PERL / 4;
-        static_assert(PERL % 4 == 0, "16-byte accesses");
-        const float kLog2e = 1.4426950408889634f;
         const float *bwd_chunk = bwd_in + (size_t)chunk * (size_t)(T + 1) * NS;
-        // the softmax offset: the maximum of fwd + bwd at row 0 (fwd is zero there); the log
-        // partition function is the same for every row, so every exponent stays in range
-        float m0 = -3.0e38f;
-        for (int st = lane; st < NS; st += 32) m0 = fmaxf(m0, bwd_chunk[st]);
-        m0 = ofd::warp_max(m0);
-        float4 b[NV];
-        auto fetch = [&](int r) {
-#pragma unroll
-            for (int q = 0; q < NV; ++q)
-                b[q] = *reinterpret_cast<const float4 *>(bwd_chunk + (size_t)r * NS + (q * 32 + lane) * 4);
-        };
-        auto emit = [&](int r) {  // b holds backward row r
-            const float *fr = sm.alpha[r % 3];
-            float e[PERL];
-            float part = 0.f;
-#pragma unroll
-            for (int q = 0; q < NV; ++q) {
-                const float4 f = *reinterpret_cast<const float4 *>(fr + (q * 32 + lane) * 4);
-                const float fv[4] = {f.x, f.y, f.z, f.w}, bv[4] = {b[q].x, b[q].y, b[q].z, b[q].w};
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    e[q * 4 + k] = ofd::ex2_approx(((fv[k] + bv[k]) - m0) * kLog2e);
-                    part += e[q * 4 + k];
-                }
-            }
-#pragma unroll
-            for (int o = 16; o; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-            const float inv = 1.0f / part;
-            float *pr = out_chunk + (size_t)r * NS;
-#pragma unroll
-            for (int q = 0; q < NV; ++q)
-                *reinterpret_cast<float4 *>(pr + (q * 32 + lane) * 4) =
-                    make_float4(e[q * 4] * inv, e[q * 4 + 1] * inv, e[q * 4 + 2] * inv, e[q * 4 + 3] * inv);
-        };
+        const float m0 = PosteriorRow<NS>::row_max(bwd_chunk, lane);
+        PosteriorRow<NS> pr;
+        auto fetch = [&](int r) { pr.fetch(bwd_chunk + (size_t)r * NS, lane); };
+        auto emit = [&](int r) { pr.emit(sm.alpha[r % 3], out_chunk + (size_t)r * NS, m0, lane); };
         fetch(0);
         __syncthreads();  // start of the scan
         int next_row = 0;
@@ -567,9 +630,21 @@ scan_kernel(const __half *__restrict__ scores, float *__restrict__ bwd, float *_
             int T, int N, int n_bwd_blocks, float stay, const ofx::Tables *__restrict__ tables, int *status) {
     extern __shared__ unsigned char smem_raw[];
     if ((int)blockIdx.x < n_bwd_blocks)
-        scan_body<BwdTopo<NS>, NS, SPT, CPB, RING>(smem_raw, blockIdx.x, scores, bwd, T, N, stay, tables, status);
+        scan_body<BwdTopo<NS>, NS, SPT, CPB, RING, false>(smem_raw, blockIdx.x, scores, bwd, nullptr, T, N, stay,
+                                                          tables, status);
     else
-        scan_body<FwdTopo<NS>, NS, SPT, CPB, RING>(smem_raw, blockIdx.x - n_bwd_blocks, scores, fwd, T, N, stay, tables, status);
+        scan_body<FwdTopo<NS>, NS, SPT, CPB, RING, false>(smem_raw, blockIdx.x - n_bwd_blocks, scores, fwd, nullptr,
+                                                          T, N, stay, tables, status);
+}
+
+// Forward scan with the posterior on top (plain variant).
+template <int NS, int SPT, int CPB, int RING>
+__global__ void __launch_bounds__((NS / SPT) * CPB + 64, (NS >= 1024 ? 2 : 1))
+scan_posterior_kernel(const __half *__restrict__ scores, const float *__restrict__ bwd, float *__restrict__ post,
+                      int T, int N, float stay, const ofx::Tables *__restrict__ tables, int *status) {
+    extern __shared__ unsigned char smem_raw[];
+    scan_body<FwdTopo<NS>, NS, SPT, CPB, RING, true>(smem_raw, blockIdx.x, scores, post, bwd, T, N, stay, tables,
+                                                     status);
 }
 
 template <int NS, int SPT, int RING>
@@ -624,6 +699,18 @@ cudaError_t launch_spec(const __half *scores, float *bwd, float *fwd, int T, int
     return cudaGetLastError();
 }
 
+template <int NS, int SPT, int CPB, int RING>
+cudaError_t launch_posterior(const __half *scores, const float *bwd, float *post, int T, int N, float stay,
+                             const ofx::Tables *tables, int *status, cudaStream_t stream) {
+    using Smem = ScanSmem<NS, CPB, RING>;
+    const size_t bytes = sizeof(Smem) + 128;
+    auto kern = scan_posterior_kernel<NS, SPT, CPB, RING>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) return e;
+    kern<<<(N + CPB - 1) / CPB, (NS / SPT) * CPB + 64, bytes, stream>>>(scores, bwd, post, T, N, stay, tables, status);
+    return cudaGetLastError();
+}
+
 template <int NS, int SPT, int RING>
 cudaError_t launch_spec_posterior(const __half *scores, const float *bwd, float *post, int T, int N, float stay,
                                   const ofx::Tables *tables, int *status, cudaStream_t stream) {
@@ -638,14 +725,20 @@ cudaError_t launch_spec_posterior(const __half *scores, const float *bwd, float 
 
 }  // namespace
 
-bool of_forward_posterior_fused(int state_len) { return state_len == 4; }
+// (Not for the 64-state model: a row is too little work there for a warp-wide reduction per
+// chunk and timestep to pay; its posterior is done by the stand-alone loop.)
+bool of_forward_posterior_fused(int state_len) { return state_len == 4 || state_len == 5; }
 
 cudaError_t of_launch_forward_posterior(const void *scores_fp16, const float *bwd, float *post, int T, int N,
                                         int state_len, float stay, const ofx::Tables *tables, int *status,
                                         cudaStream_t stream) {
-    if (state_len != 4 || T < 1) return cudaErrorInvalidValue;
-    return launch_spec_posterior<256, 4, 6>(static_cast<const __half *>(scores_fp16), bwd, post, T, N, stay, tables,
-                                            status, stream);
+    const __half *s = static_cast<const __half *>(scores_fp16);
+    if (T < 1) return cudaErrorInvalidValue;
+    switch (state_len) {
+        case 4: return launch_spec_posterior<256, 4, 6>(s, bwd, post, T, N, stay, tables, status, stream);
+        case 5: return launch_posterior<1024, 2, 1, 6>(s, bwd, post, T, N, stay, tables, status, stream);
+        default: return cudaErrorInvalidValue;
+    }
 }
 
 cudaError_t of_launch_scans(const void *scores_fp16, float *bwd, float *fwd, int T, int N,
