@@ -38,7 +38,8 @@ struct GpuBuf {
                            // 5 fwd scan start, 6 fwd scan done
     int *d_init_kmers;     // inside the beam_vector allocation, behind the back-pointers
     ofx::Tables *d_tables;
-    float *d_fwd;              // forward scores [N][T+1][ns]: scan kernel -> posterior kernel
+    float *d_fwd;              // forward scores [N][T+1][ns]: scan kernel -> posterior kernel (64-state model
+                               // only; null otherwise: the forward scan kernel writes the posterior)
     int *d_status;
     unsigned char *d_results;  // moves | sequence | qstring, N*T bytes each
     unsigned char *h_stage;    // page-locked, 3*N*T bytes + one status word
@@ -222,7 +223,7 @@ extern "C" int ofb_decode_submit(int T, int N, int C, const void *scores, int st
 
     // stream:  backward scan -> beam search ----------------------> posterior + sequence -> copies
     // stream2:                  forward scan (beside the beam search) --^
-    // (for hac the forward scan kernel also writes the posterior, and a.fwd is null)
+    // (for hac and sup the forward scan kernel also writes the posterior, and a.fwd is null)
     CU(cudaEventRecord(g->ev[0], g->stream));
     CU(of_launch_scans(scores, g->pub.bwd_NTC, nullptr, T, N, state_len, blank_score, g->d_tables,
                        g->d_status, g->stream));

@@ -1,4 +1,4 @@
-// scan.cu -- backward and forward scans of the CRF-CTC decode for sm_100a, one launch for both.
+// scan.cu -- backward and forward scans (and the posterior) of the CRF-CTC decode for sm_100a.
 //
 // Replaces the reference kernel bwd_scan (src/scan_cuda.cu:8-57) and the recursion half of
 // fwd_post_scan (src/scan_cuda.cu:59-146), and reproduces the CPU routines backward_scan and
@@ -9,8 +9,10 @@
 //                                       for s = 4j + k                         (b = 0..3 in both)
 // The two recursions do not depend on each other (only the posterior needs both).  The launcher
 // takes either or both; the decode runs the backward scan first (the beam search waits for it)
-// and the forward scan beside the beam search, which leaves most issue slots free.  Forward
-// scores go to HBM for the kernel that forms the posterior.
+// and the forward scan beside the beam search, which leaves most issue slots free.  For the 256-
+// and 1024-state models the forward scan also forms the posterior (a warp of its own per block,
+// see PosteriorRow) and its scores never leave the chip; for the 64-state model they go to HBM for
+// the kernel that forms the posterior.
 //
 // Shape of a block.  In either direction the four states that share j also share their four
 // neighbour inputs, and their 16 transition scores are one contiguous 32-byte piece of the score
