@@ -148,6 +148,54 @@ def test_into_and_submit_wait_match_decode_gpu(native_lib):
     gb.free()
 
 
+def test_decodes_from_several_host_threads_and_in_flight(native_lib):
+    # a gpubuf per host thread, as the reference's driver does it (src/main.c:23,207): decodes of
+    # different batches running at the same time must not disturb each other; nor must two
+    # decodes submitted back to back on two gpubufs from one thread
+    import threading
+    import torch
+    from openfish_b200 import synth
+    of = native_lib
+    shapes = [(3, 700, 9), (4, 500, 6), (5, 120, 2), (4, 333, 5)]
+    sc = [torch.from_numpy(synth.make_scores(T, N, sl, 130 + i)).cuda() for i, (sl, T, N) in enumerate(shapes)]
+    alone = [of.decode_gpu(x, sl) for x, (sl, T, N) in zip(sc, shapes)]
+    got, errs = [None] * len(shapes), []
+
+    def work(i):
+        try:
+            torch.cuda.set_device(0)
+            sl, T, N = shapes[i]
+            gb = of.gpubuf_init(T, N, sl)
+            for _ in range(5):
+                got[i] = of.decode_gpu(sc[i], sl, gpubuf=gb)
+            gb.free()
+        except Exception as exc:
+            errs.append(exc)
+
+    th = [threading.Thread(target=work, args=(i,)) for i in range(len(shapes))]
+    for t in th:
+        t.start()
+    for t in th:
+        t.join()
+    assert not errs, errs
+    for a, b in zip(alone, got):
+        for k in ("moves", "sequence", "qstring"):
+            assert np.array_equal(a[k], b[k]), k
+
+    gbs = [of.gpubuf_init(T, N, sl) for sl, T, N in shapes]
+    outs = [[torch.zeros((N, T), dtype=torch.uint8).pin_memory() for _ in range(3)] for sl, T, N in shapes]
+    for _ in range(3):
+        for i, (sl, T, N) in enumerate(shapes):
+            of.decode_into(sc[i], sl, gbs[i], *outs[i], wait=False)
+        for g in gbs:
+            of.decode_wait(g)
+    for a, o in zip(alone, outs):
+        for k, t in zip(("moves", "sequence", "qstring"), o):
+            assert np.array_equal(a[k], t.numpy()), k
+    for g in gbs:
+        g.free()
+
+
 def test_argument_errors(native_lib):
     import torch
     of = native_lib
