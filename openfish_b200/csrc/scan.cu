@@ -218,7 +218,9 @@ struct PosteriorRow {
 };
 
 // ------------------------------------------------------------------------------------------
-// Plain variant: CPB chunks per block; uncertified states are settled within the timestep.
+// Plain variant (the 64-state model: two chunks per block, too little work per timestep for the
+// speculative machinery to pay): CPB chunks per block; uncertified states are settled within the
+// timestep.
 
 template <int NS, int CPB, int RING>
 struct ScanSmem {
@@ -233,19 +235,13 @@ struct ScanSmem {
     int abort_flag;
 };
 
-// POST (forward direction only): the rows are not written out; one more warp turns each row
-// into the posterior row and writes that (`out` is then the posterior tensor and `bwd_in` the
-// finished backward scores).  Row i is complete when timestep i starts and its buffer is written
-// again in timestep i+1, so the posterior warp takes it during timestep i, beside the scan warps
-// that read it too; the last row is taken after the scan.
-template <class Topo, int NS, int SPT, int CPB, int RING, bool POST>
+template <class Topo, int NS, int SPT, int CPB, int RING>
 __device__ __forceinline__ void scan_body(unsigned char *smem_raw, int block, const __half *scores,
-                                          float *out, const float *bwd_in, int T, int N, float stay,
+                                          float *out, int T, int N, float stay,
                                           const ofx::Tables *tables, int *status) {
     constexpr int NJ = NS / 4;
     constexpr int TPC = NS / SPT;
     static_assert(TPC % 32 == 0, "a warp must not straddle two chunks");
-    static_assert(!POST || Topo::kForward, "the posterior rides on the forward scan");
     using Smem = ScanSmem<NS, CPB, RING>;
     Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
 
@@ -274,33 +270,6 @@ __device__ __forceinline__ void scan_body(unsigned char *smem_raw, int block, co
     // the scans address scores as [T][N][4ns] whatever C is (src/decode_cpu.c:16-18,27,59-62,80)
     const size_t t_stride = (size_t)N * NS * 4;
     const __half *blk_scores = scores + (size_t)chunk0 * NS * 4;
-
-    if (POST && tid >= TPC * CPB + 32) {
-        // ------------------------------------------------------------------ posterior warp
-        const int lane = tid & 31;
-        PosteriorRow<NS> pr[CPB];
-        float m0[CPB];
-        const float *bwd_blk = bwd_in + (size_t)chunk0 * (size_t)(T + 1) * NS;
-        float *post_blk = out + (size_t)chunk0 * (size_t)(T + 1) * NS;
-#pragma unroll
-        for (int c = 0; c < CPB; ++c)
-            if (c < nlive) {
-                m0[c] = PosteriorRow<NS>::row_max(bwd_blk + (size_t)c * (T + 1) * NS, lane);
-                pr[c].fetch(bwd_blk + (size_t)c * (T + 1) * NS, lane);
-            }
-        __syncthreads();  // start of the scan
-        for (int i = 0; i <= T; ++i) {
-#pragma unroll
-            for (int c = 0; c < CPB; ++c)
-                if (c < nlive) {
-                    const size_t row = ((size_t)c * (T + 1) + i) * NS;
-                    pr[c].emit(sm.alpha[i & 1][c], post_blk + row, m0[c], lane);
-                    if (i < T) pr[c].fetch(bwd_blk + row + NS, lane);
-                }
-            if (i < T) __syncthreads();  // end of timestep i
-        }
-        return;
-    }
 
     if (tid >= TPC * CPB) {
         // ------------------------------------------------------------------ copy warp
@@ -336,7 +305,7 @@ __device__ __forceinline__ void scan_body(unsigned char *smem_raw, int block, co
     const bool live = chunk < N;
     const ofx::TabRef tr = {sm.exp2_rep + (tid & (kExpCopies - 1)), kExpCopies, sm.rcp_c, sm.log_c};
     float *out_chunk = out + (size_t)(live ? chunk : 0) * (size_t)(T + 1) * NS;
-    if (live && !POST) {
+    if (live) {
 #pragma unroll
         for (int k = 0; k < SPT; ++k) out_chunk[(size_t)Topo::zero_row(T) * NS + Topo::state(j, k0 + k)] = 0.f;
     }
@@ -352,13 +321,13 @@ __device__ __forceinline__ void scan_body(unsigned char *smem_raw, int block, co
             ofd::lse5_batch<SPT>(v, res, tr);
         }
         thread_store<Topo, SPT>(sm.alpha[(i & 1) ^ 1][cl], out_chunk + (size_t)Topo::out_row(i, T) * NS, j, k0,
-                                res, live && !POST);
+                                res, live);
         __syncthreads();  // row complete; the copy warp has confirmed the next score row
     }
 }
 
 // ------------------------------------------------------------------------------------------
-// Speculative variant (one chunk per block).
+// Speculative variant (one chunk per block; the 256- and 1024-state models).
 //
 // In the plain variant a state whose rounding the fp32 evaluation cannot certify sends its whole
 // warp through the value-exact routine before the timestep can end, and almost every timestep
@@ -632,21 +601,10 @@ scan_kernel(const __half *__restrict__ scores, float *__restrict__ bwd, float *_
             int T, int N, int n_bwd_blocks, float stay, const ofx::Tables *__restrict__ tables, int *status) {
     extern __shared__ unsigned char smem_raw[];
     if ((int)blockIdx.x < n_bwd_blocks)
-        scan_body<BwdTopo<NS>, NS, SPT, CPB, RING, false>(smem_raw, blockIdx.x, scores, bwd, nullptr, T, N, stay,
-                                                          tables, status);
+        scan_body<BwdTopo<NS>, NS, SPT, CPB, RING>(smem_raw, blockIdx.x, scores, bwd, T, N, stay, tables, status);
     else
-        scan_body<FwdTopo<NS>, NS, SPT, CPB, RING, false>(smem_raw, blockIdx.x - n_bwd_blocks, scores, fwd, nullptr,
-                                                          T, N, stay, tables, status);
-}
-
-// Forward scan with the posterior on top (plain variant).
-template <int NS, int SPT, int CPB, int RING>
-__global__ void __launch_bounds__((NS / SPT) * CPB + 64, (NS >= 1024 ? 2 : 1))
-scan_posterior_kernel(const __half *__restrict__ scores, const float *__restrict__ bwd, float *__restrict__ post,
-                      int T, int N, float stay, const ofx::Tables *__restrict__ tables, int *status) {
-    extern __shared__ unsigned char smem_raw[];
-    scan_body<FwdTopo<NS>, NS, SPT, CPB, RING, true>(smem_raw, blockIdx.x, scores, post, bwd, T, N, stay, tables,
-                                                     status);
+        scan_body<FwdTopo<NS>, NS, SPT, CPB, RING>(smem_raw, blockIdx.x - n_bwd_blocks, scores, fwd, T, N, stay, tables,
+                                                   status);
 }
 
 template <int NS, int SPT, int RING>
@@ -701,18 +659,6 @@ cudaError_t launch_spec(const __half *scores, float *bwd, float *fwd, int T, int
     return cudaGetLastError();
 }
 
-template <int NS, int SPT, int CPB, int RING>
-cudaError_t launch_posterior(const __half *scores, const float *bwd, float *post, int T, int N, float stay,
-                             const ofx::Tables *tables, int *status, cudaStream_t stream) {
-    using Smem = ScanSmem<NS, CPB, RING>;
-    const size_t bytes = sizeof(Smem) + 128;
-    auto kern = scan_posterior_kernel<NS, SPT, CPB, RING>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-    if (e != cudaSuccess) return e;
-    kern<<<(N + CPB - 1) / CPB, (NS / SPT) * CPB + 64, bytes, stream>>>(scores, bwd, post, T, N, stay, tables, status);
-    return cudaGetLastError();
-}
-
 template <int NS, int SPT, int RING>
 cudaError_t launch_spec_posterior(const __half *scores, const float *bwd, float *post, int T, int N, float stay,
                                   const ofx::Tables *tables, int *status, cudaStream_t stream) {
@@ -738,7 +684,7 @@ cudaError_t of_launch_forward_posterior(const void *scores_fp16, const float *bw
     if (T < 1) return cudaErrorInvalidValue;
     switch (state_len) {
         case 4: return launch_spec_posterior<256, 4, 6>(s, bwd, post, T, N, stay, tables, status, stream);
-        case 5: return launch_posterior<1024, 2, 1, 6>(s, bwd, post, T, N, stay, tables, status, stream);
+        case 5: return launch_spec_posterior<1024, 4, 6>(s, bwd, post, T, N, stay, tables, status, stream);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -750,7 +696,7 @@ cudaError_t of_launch_scans(const void *scores_fp16, float *bwd, float *fwd, int
     switch (state_len) {
         case 3: return launch<64, 1, 2, 8>(s, bwd, fwd, T, N, stay, tables, status, stream);
         case 4: return launch_spec<256, 4, 6>(s, bwd, fwd, T, N, stay, tables, status, stream);
-        case 5: return launch<1024, 2, 1, 6>(s, bwd, fwd, T, N, stay, tables, status, stream);
+        case 5: return launch_spec<1024, 4, 6>(s, bwd, fwd, T, N, stay, tables, status, stream);
         default: return cudaErrorInvalidValue;
     }
 }
