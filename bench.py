@@ -188,8 +188,7 @@ def run_reference(args, rank, world):
     if rank != 0:
         return
     cores = os.cpu_count() or 1
-    n = max(cores, min(N_PER_GPU, 2 * cores))  # a bounded sample of the workload per step
-    n = min(n, N_PER_GPU)
+    n = min(N_PER_GPU, max(cores, 256))  # a bounded sample of the workload per step (about a second)
     sc = host_sample(n, SEED)
     for _ in range(max(0, min(args.warmup, 1))):
         cpu_decode_rate(sc, cores)
