@@ -121,7 +121,7 @@ class ClockSampler(threading.Thread):
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
-def measure_rotary(of, dev):
+def measure_rotary(of, dev, cpu_too=False):
     """openfish_rotary_emb_gpu on fp16 [32][1666][3][8][64] (Q and K heads in one call): device time
     by the library's CUDA events on the legacy default stream the kernel runs on, rotating over four tensors
     (655 MB) so that no call finds its input in the 126 MB L2."""
@@ -147,9 +147,27 @@ def measure_rotary(of, dev):
     ms = total / reps
     nbytes = 2 * B * S * 2 * H * D * 2 + 2 * S * half * 4
     peak, _ = measured_peak()
-    return {"shape": "fp16 [32][1666][3][8][64], nheads=16", "ms": ms, "algorithmic_bytes": nbytes,
+    out = {"shape": "fp16 [32][1666][3][8][64], nheads=16", "ms": ms, "algorithmic_bytes": nbytes,
             "achieved_gbs": nbytes / (ms * 1e-3) / 1e9, "frac_of_measured_hbm": nbytes / (ms * 1e-3) / 1e9 / peak,
             "call_wall_ms": 1e3 * wall / reps, "calls": reps}
+    if cpu_too:
+        # the reference's CPU routine on the same values widened to float32 (it works on float32),
+        # all host cores (it caps its threads at the batch size, src/nn_cpu.c:95)
+        import oracle
+        x32 = xs[0].float().cpu().numpy().reshape(-1)
+        cores = os.cpu_count() or 1
+        fn, kind = (oracle.ref_rotary, "reference") if oracle.have_ref() else (None, "port")
+        best = None
+        for _ in range(3):
+            t0 = time.perf_counter()
+            if fn:
+                fn(x32, sin.cpu().numpy(), cos.cpu().numpy(), half, S * 3 * H * D, 3 * H * D, D, B, S, 2 * H, cores)
+            else:
+                oracle.rotary(x32, sin.cpu().numpy(), cos.cpu().numpy(), half, S * 3 * H * D, 3 * H * D, D, B, S, 2 * H)
+            dt = time.perf_counter() - t0
+            best = dt if best is None else min(best, dt)
+        out["cpu_baseline"] = {"ms": 1e3 * best, "kind": kind, "cores": min(cores, B) if fn else 1}
+    return out
 
 
 def physical_gpu_index(local_rank):
@@ -349,7 +367,7 @@ def main():
         a0 = time.perf_counter()
         of.decode_gpu(scores, STATE_LEN, gpubuf=gb)
         api_wall.append(1e3 * (time.perf_counter() - a0))
-    rotary = measure_rotary(of, dev) if rank == 0 else None
+    rotary = measure_rotary(of, dev, cpu_too=(world == 1 and not args.no_cpu_baseline)) if rank == 0 else None
 
     if rank == 0:
         peak, peak_src = measured_peak()
