@@ -361,6 +361,9 @@ struct SpecSmem {
     int n_wrong[2];
     unsigned short wrong_state[NW * kPerWarp];
     float wrong_value[NW * kPerWarp];
+    // settle-now path: a warp's uncertified states, dealt out to its lanes, and their exact values
+    unsigned short redo_state[NW][32 * SPT];
+    float redo_value[NW][32 * SPT];
     int abort_flag;
 };
 
@@ -570,10 +573,36 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
                 total += __popc(bad[k]);
             }
         }
-        if (total > PER) {
-            // many uncertified states (the first few hundred timesteps, where scores are small
-            // and the float grid fine): settle them here and now, nothing to check later
-            ofd::lse5_batch<SPT>(v, res, tr);
+        if (total > 16 * SPT) {
+            // most states uncertified (the first few dozen timesteps, where scores are small and
+            // the float grid fine): the exact routine for every state, straight from registers
+            ofx::lse5_batch_exact<SPT>(v, res, tr);
+            total = 0;
+        } else if (total > PER) {
+            // many uncertified states (the next hundred or two timesteps): settle them here and
+            // now, nothing to check later.  They are dealt out evenly to the warp's lanes, so the
+            // exact routine runs ceil(total / 32) times rather than once per state of the
+            // unluckiest lane.
+            int pos[SPT], base = 0;
+#pragma unroll
+            for (int k = 0; k < SPT; ++k) {
+                pos[k] = base + __popc(bad[k] & lt_mask);
+                if (!ok[k]) sm.redo_state[warp][pos[k]] = (unsigned short)Topo::state(j, k0 + k);
+                base += __popc(bad[k]);
+            }
+            __syncwarp();
+            for (int first = 0; first < total; first += 32) {
+                const int e = first + lane;
+                const int st = sm.redo_state[warp][e < total ? e : 0];
+                float w[5];
+                terms_of<Topo>(st, sm.alpha[i % 3], sm.ring[i % RING], stay, w);
+                const float x = ofx::lse5_exact(w, tr);
+                if (e < total) sm.redo_value[warp][e] = x;
+            }
+            __syncwarp();
+#pragma unroll
+            for (int k = 0; k < SPT; ++k)
+                if (!ok[k]) res[k] = sm.redo_value[warp][pos[k]];
             total = 0;
         } else if (total) {
             int base = 0;
