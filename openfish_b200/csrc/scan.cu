@@ -349,7 +349,7 @@ template <int NS, int SPT, int RING>
 struct SpecSmem {
     static constexpr int kRowBytes = NS * 4 * 2;
     static constexpr int NW = NS / SPT / 32;  // scan warps
-    static constexpr int kPerWarp = 8;        // listed states per warp and timestep, at most
+    static constexpr int kPerWarp = 16;       // listed states per warp and timestep, at most
     alignas(128) unsigned char ring[RING][kRowBytes];
     alignas(16) float alpha[3][NS];
     alignas(16) double exp2_rep[ofx::kExpTab * kExpCopies];
