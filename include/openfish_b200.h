@@ -30,7 +30,8 @@ enum openfish_b200_status {
     OPENFISH_B200_ERR_DEVICE_WAIT = 7, /* a kernel gave up waiting for an asynchronous copy */
     OPENFISH_B200_ERR_NO_CPU_PATH = 8, /* openfish_decode_cpu / openfish_rotary_emb_cpu called */
     OPENFISH_B200_ERR_TOO_LONG = 9,    /* T beyond what one block's shared memory can trace back */
-    OPENFISH_B200_ERR_SCRATCH_LIMIT = 10 /* shape needs more than the static scratch array holds */
+    OPENFISH_B200_ERR_SCRATCH_LIMIT = 10, /* shape needs more than the static scratch array holds */
+    OPENFISH_B200_ERR_ARITH = 11       /* this GPU's ex2/lg2 approximations exceed the assumed error bounds */
 };
 
 /* 0 (default): behave like the reference -- print the error and exit(EXIT_FAILURE).
@@ -73,6 +74,18 @@ void openfish_b200_last_decode_detail_ms(const openfish_gpubuf_t *gpubuf, float 
 /* Device time, in milliseconds, of the calling thread's last openfish_rotary_emb_gpu call (CUDA
  * events on the legacy default stream around the kernel). */
 float openfish_b200_last_rotary_ms(void);
+
+/* Self-check of the arithmetic the scans rely on.  Backward scores are made bit-identical to the
+ * reference CPU decoder's by an fp32 evaluation that certifies its own result, with an exact FP64
+ * routine behind it; the certificate rests on error bounds of two hardware approximations.  This
+ * call measures them on the current GPU over their whole domains (about a second): err[0] = largest
+ * relative error of ex2.approx.ftz.f32 on [-126, 0], err[1] = largest absolute error of
+ * lg2.approx.ftz.f32 on [1, 8).  Returns OK when both are within the bounds below, ERR_ARITH when
+ * not (results could then differ from the reference's in the last bit), ERR_CUDA/ERR_ALLOC on
+ * failure.  Does not touch openfish_b200_last_status().  No counterpart in the reference. */
+#define OPENFISH_B200_EX2_REL_BOUND 2.384185791015625e-07 /* 2^-22 */
+#define OPENFISH_B200_LG2_ABS_BOUND 2.828e-07             /* 2^-21.75 */
+int openfish_b200_selfcheck_arith(double err[2]);
 
 /* Number of kernels one decode call launches (for benchmark bookkeeping). */
 int openfish_b200_kernels_per_decode(void);

@@ -15,7 +15,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("OPENFISH_B200_LIB") or os.path.join(_HERE, "lib", "libopenfish.so")
 
 STATUS_NAMES = ["OK", "ERR_ARGUMENT", "ERR_LAYOUT", "ERR_SHAPE", "ERR_OPTION", "ERR_ALLOC",
-                "ERR_CUDA", "ERR_DEVICE_WAIT", "ERR_NO_CPU_PATH", "ERR_TOO_LONG", "ERR_SCRATCH_LIMIT"]
+                "ERR_CUDA", "ERR_DEVICE_WAIT", "ERR_NO_CPU_PATH", "ERR_TOO_LONG", "ERR_SCRATCH_LIMIT",
+                "ERR_ARITH"]
 STATIC_SCRATCH_BYTES = 48 << 20
 
 
@@ -87,6 +88,8 @@ def lib():
         L.openfish_b200_set_error_mode.argtypes = [i]
         L.openfish_b200_kernels_per_decode.restype = i
         L.openfish_b200_last_rotary_ms.restype = C.c_float
+        L.openfish_b200_selfcheck_arith.restype = i
+        L.openfish_b200_selfcheck_arith.argtypes = [C.POINTER(C.c_double)]
         L.openfish_b200_decode_static.restype = i
         L.openfish_b200_decode_static.argtypes = [i, i, i, vp, i, C.POINTER(Opt), vp, vp, vp]
         L.get_openfish_log_level.restype = i
@@ -218,6 +221,14 @@ def rotary_emb_gpu(x_gpu, sin_gpu, cos_gpu, batch_size, seqlen, nheads, head_dim
                                   batch_size, seqlen, nheads, head_dim, rotary_half, stride_batch,
                                   stride_seq, stride_head)
     _check()
+
+
+def selfcheck_arith():
+    """openfish_b200_selfcheck_arith: (status, ex2 relative error, lg2 absolute error) measured on
+    the current GPU."""
+    err = (C.c_double * 2)()
+    st = lib().openfish_b200_selfcheck_arith(err)
+    return st, err[0], err[1]
 
 
 def last_rotary_ms():

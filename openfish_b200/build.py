@@ -15,7 +15,8 @@ LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libopenfish.so")
 CLI_SRC = os.path.join(HERE, "cli", "openfish_cli.c")
 CLI = os.path.join(HERE, "bin", "openfish")  # the command-line driver, linked against LIB
-CU = ["scan.cu", "beam_search.cu", "posterior_seq.cu", "rotary.cu", "decode_b200.cu", "decode_static.cu"]
+CU = ["scan.cu", "beam_search.cu", "posterior_seq.cu", "rotary.cu", "decode_b200.cu", "decode_static.cu",
+      "selfcheck.cu"]
 CC = ["openfish_api.c"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -31,6 +31,10 @@ int ofb_rotary(void *x, const void *sin_t, const void *cos_t, int batch, int seq
                int rotary_half, long long stride_batch, long long stride_seq,
                long long stride_head);
 
+/* Measured error of the two hardware approximations the certified fp32 arithmetic relies on:
+ * err[0] ex2.approx (relative, arguments in [-126, 0]), err[1] lg2.approx (absolute, [1, 8)). */
+int ofb_selfcheck_arith(double err[2]);
+
 /* Device time of the calling thread's last ofb_rotary call, in milliseconds. */
 float ofb_last_rotary_ms(void);
 

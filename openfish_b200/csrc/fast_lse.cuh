@@ -1,7 +1,7 @@
 // fast_lse.cuh -- fp32 evaluation of the reference's five-term log-sum-exp that knows when it
 // is right.
 //
-// The value-exact routine in exact_math.cuh costs about 60 FP64 operations per state and
+// The value-exact routine in exact_math.cuh costs about 63 FP64 operations per state and
 // timestep.  Most of the time that effort is not needed to know which float the reference
 // arithmetic produces: the result max + log(sum) is rounded to a float whose spacing grows with
 // the magnitude of the scores (2^-12 once they pass 2048), while log(sum) can be had in fp32
@@ -13,13 +13,15 @@
 // accepted.
 //
 // Error budget of log(sum), all relative to sum >= 1 (so also absolute in the logarithm):
-//   ex2.approx: 2 ulp                                   2^-22
+//   ex2.approx: 2 ulp (documented; 2^-22.7 measured)     2^-22
 //   rounding of (v-m)*log2(e) before ex2, weighted
 //     by the term's size (max a*exp(-a) = 0.37, 4 terms) 2^-23.4
 //   four float additions here                           2^-22
 //   the reference's four float additions (decode_cpu.c:47) 2^-22
-//   lg2.approx on [1,2): 2^-22 absolute in log2         2^-22.5
-//   q + lg2(f), * ln2, the +-eps additions: float roundings  < 2^-21.5 together
+//   lg2.approx on [1,8): at most 2^-21.75 absolute in log2, its own rounding included (measured
+//     over every float of the interval: 2^-21.78; openfish_b200_selfcheck_arith repeats the
+//     measurement on the GPU at hand and compares with this bound)            2^-22.28
+//   * ln2, the +-eps additions: float roundings           < 2^-22.5 together
 // Sum < 2^-19.9; kLseEps = 2^-19.5 leaves a margin of a third.
 #pragma once
 #include <cuda_runtime.h>
@@ -39,15 +41,10 @@ __device__ __forceinline__ float lg2_approx(float x) {
     return y;
 }
 
-// ln of s in [1, 8): the power of two is split off so that lg2 works on [1,2), where its error is
-// absolute.  The exponent becomes a float through the 2^23 trick (an integer add and a float
-// subtraction) rather than a conversion instruction.
+// ln of s in [1, 8).
 __device__ __forceinline__ float ln_1to8(float s) {
     const float kLn2 = 0.6931471805599453f;
-    const unsigned bits = __float_as_uint(s);
-    const float q = __uint_as_float(0x4b000000u | (bits >> 23)) - 8388735.0f;  // (2^23 + e) - (2^23 + 127)
-    const float f = __uint_as_float((bits & 0x007fffffu) | 0x3f800000u);
-    return (q + lg2_approx(f)) * kLn2;
+    return lg2_approx(s) * kLn2;
 }
 
 // v: the five terms.  On success writes the reference-exact float to `out`.
@@ -64,8 +61,8 @@ __device__ __forceinline__ bool lse5_try_fast(const float v[5], float &out) {
     const float hi = m + (l + kLseEps);
     out = lo;
     // A NaN or infinite term makes the sum NaN (an infinite maximum gives inf - inf in its own
-    // term); ln_1to8 works on the bits and would not pass that on, so the sum is tested itself.
-    return lo == hi && s < 8.f;
+    // term), the logarithm and both ends with it, and NaN compares unequal.
+    return lo == hi;
 }
 
 }  // namespace ofd
@@ -99,7 +96,7 @@ __device__ __forceinline__ void lse5_fast_guess(const float (*v)[5], float *out,
         const float lo = m[k] + (l[k] - kLseEps);
         const float hi = m[k] + (l[k] + kLseEps);
         out[k] = m[k] + l[k];
-        ok[k] = lo == hi && s[k] < 8.f;  // (the second test fails for a NaN sum)
+        ok[k] = lo == hi;  // (a NaN sum makes both ends NaN: never accepted)
     }
 }
 
@@ -140,7 +137,7 @@ __device__ __forceinline__ void lse5_batch(const float (*v)[5], float *out, cons
             const float lo = m[k] + (l[k] - kLseEps);
             const float hi = m[k] + (l[k] + kLseEps);
             out[k] = lo;
-            ok[k] = lo == hi && s[k] < 8.f;  // (the second test fails for a NaN sum)
+            ok[k] = lo == hi;  // (a NaN sum makes both ends NaN: never accepted)
         }
     }
     int nbad = 0;

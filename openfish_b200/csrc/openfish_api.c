@@ -220,6 +220,13 @@ void openfish_rotary_emb_gpu(void *x_gpu, void *sin_gpu, void *cos_gpu, int batc
 
 float openfish_b200_last_rotary_ms(void) { return ofb_last_rotary_ms(); }
 
+int openfish_b200_selfcheck_arith(double err[2]) {
+    const int rc = ofb_selfcheck_arith(err);
+    if (rc != OPENFISH_B200_OK) return rc;
+    return (err[0] <= OPENFISH_B200_EX2_REL_BOUND && err[1] <= OPENFISH_B200_LG2_ABS_BOUND) ? OPENFISH_B200_OK
+                                                                                           : OPENFISH_B200_ERR_ARITH;
+}
+
 void openfish_decode_cpu(const int T, const int N, const int C, int nthreads, void *scores_TNC,
                          const int state_len, const openfish_opt_t *options, uint8_t **moves,
                          char **sequence, char **qstring) {

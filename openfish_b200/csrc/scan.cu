@@ -652,7 +652,7 @@ scan_spec_kernel(const __half *__restrict__ scores, float *__restrict__ bwd, flo
 
 // Forward scan with the posterior on top: one block per chunk, reads the finished backward scores.
 template <int NS, int SPT, int RING>
-__global__ void __launch_bounds__(NS / SPT + 96)
+__global__ void __launch_bounds__(NS / SPT + 96, (NS <= 256 ? 5 : 2))
 scan_spec_posterior_kernel(const __half *__restrict__ scores, const float *__restrict__ bwd,
                            float *__restrict__ post, int T, int N, float stay,
                            const ofx::Tables *__restrict__ tables, int *status) {

@@ -263,3 +263,11 @@ def test_full_size_hac_properties_and_sampled_parity(native_lib, oracle_mod):
     ref = oracle_mod.decode(sub16.astype(np.float32), sl, nthreads=16, tensors=True)
     rep = compare(alone, ref)
     assert_parity(rep, min_identical=1.0)
+
+
+def test_hardware_approximations_are_within_the_certificates_bounds(native_lib):
+    # the certified fp32 log-sum-exp assumes error bounds of ex2.approx and lg2.approx; the library
+    # measures both over their whole domains on this GPU
+    st, ex2_rel, lg2_abs = native_lib.selfcheck_arith()
+    assert st == 0, (st, ex2_rel, lg2_abs)
+    assert 0 < ex2_rel <= 2.0 ** -22 and 0 < lg2_abs <= 2.828e-7
