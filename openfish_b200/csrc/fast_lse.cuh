@@ -12,17 +12,18 @@
 // the caller falls back to the value-exact routine.  Nothing is approximated in what is
 // accepted.
 //
-// Error budget of log(sum), all relative to sum >= 1 (so also absolute in the logarithm):
-//   ex2.approx: 2 ulp (documented; 2^-22.7 measured)     2^-22
-//   rounding of (v-m)*log2(e) before ex2, weighted
-//     by the term's size (max a*exp(-a) = 0.37, 4 terms) 2^-23.4
-//   four float additions here                           2^-22
-//   the reference's four float additions (decode_cpu.c:47) 2^-22
-//   lg2.approx on [1,8): at most 2^-21.75 absolute in log2, its own rounding included (measured
-//     over every float of the interval: 2^-21.78; openfish_b200_selfcheck_arith repeats the
-//     measurement on the GPU at hand and compares with this bound)            2^-22.28
-//   * ln2, the +-eps additions: float roundings           < 2^-22.5 together
-// Sum < 2^-19.9; kLseEps = 2^-19.5 leaves a margin of a third.
+// Error budget of log(sum), all relative to sum >= 1 (so also absolute in the logarithm), in
+// units of 1e-7:
+//   ex2.approx: 2 ulp = 2^-22 documented (2^-22.7 measured), weights sum to one        2.38
+//   rounding of (v-m)*log2(e) before ex2, weighted by the term's size
+//     (max a*exp(-a) = 0.37, 4 terms)                                                   0.88
+//   four float additions here, each relative to a partial sum                           2.38
+//   the reference's five float roundings of its running sum (decode_cpu.c:47)           2.98
+//   lg2.approx on [1,8): at most 2^-21.75 absolute in log2, its own rounding included
+//     (measured over every float of the interval: 2^-21.78), times ln 2                 1.96
+//   rounding of the product with ln 2 and of l -+ eps (l < 2)                           1.19
+// Sum 11.8 = 2^-19.7; kLseEps = 13.5 = 2^-19.5.  openfish_b200_selfcheck_arith repeats the two
+// measurements on the GPU at hand and compares them with the bounds used here.
 #pragma once
 #include <cuda_runtime.h>
 
