@@ -328,7 +328,7 @@ beam_search_kernel(const OfDecodeArgs a) {
 
         // pruning threshold (src/beam_search.c:320-381): best - ln(beam_cut); if more than 32
         // candidates pass, bisect towards 25..32 survivors for at most 9 further guesses
-        const float best = warp_max_f32(fmaxf(fmaxf(fmaxf(c0, c1), fmaxf(c2, c3)), c4));
+        const float best = warp_max_f32(ofd::max3(ofd::max3(c0, c1, c2), c3, c4));
         float cut = __fsub_rn(best, a.log_beam_cut);
         auto count_at_least = [&](float th) {
             const int n = (c0 >= th) + (c1 >= th) + (c2 >= th) + (c3 >= th) + (c4 >= th);

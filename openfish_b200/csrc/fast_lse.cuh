@@ -36,6 +36,13 @@ __device__ __forceinline__ float ex2_approx(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// maximum of three in one instruction (sm_100); a NaN operand loses against a number, as in fmaxf
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ float max5(const float v[5]) { return max3(max3(v[0], v[1], v[2]), v[3], v[4]); }
 __device__ __forceinline__ float lg2_approx(float x) {
     float y;
     asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -51,7 +58,7 @@ __device__ __forceinline__ float ln_1to8(float s) {
 // v: the five terms.  On success writes the reference-exact float to `out`.
 __device__ __forceinline__ bool lse5_try_fast(const float v[5], float &out) {
     const float kLog2e = 1.4426950408889634f;
-    const float m = fmaxf(fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3])), v[4]);
+    const float m = max5(v);
     float s = ex2_approx((v[0] - m) * kLog2e);
     s += ex2_approx((v[1] - m) * kLog2e);
     s += ex2_approx((v[2] - m) * kLog2e);
@@ -81,7 +88,7 @@ __device__ __forceinline__ void lse5_fast_guess(const float (*v)[5], float *out,
     float m[K], e[K][5], s[K], l[K];
 #pragma unroll
     for (int k = 0; k < K; ++k)
-        m[k] = fmaxf(fmaxf(fmaxf(v[k][0], v[k][1]), fmaxf(v[k][2], v[k][3])), v[k][4]);
+        m[k] = max5(v[k]);
 #pragma unroll
     for (int i = 0; i < 5; ++i)
 #pragma unroll
@@ -114,7 +121,7 @@ __device__ __forceinline__ void lse5_batch(const float (*v)[5], float *out, cons
         float m[K], e[K][5], s[K], l[K];
 #pragma unroll
         for (int k = 0; k < K; ++k)
-            m[k] = fmaxf(fmaxf(fmaxf(v[k][0], v[k][1]), fmaxf(v[k][2], v[k][3])), v[k][4]);
+            m[k] = max5(v[k]);
 #pragma unroll
         for (int i = 0; i < 5; ++i)
 #pragma unroll
