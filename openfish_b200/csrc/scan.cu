@@ -116,9 +116,11 @@ __device__ __forceinline__ void terms_of(int s, const float *in, const unsigned 
 // Terms of the SPT states (j, k0 .. k0+SPT-1) of one thread.  The 32-byte piece is read as two
 // 16-byte halves (a two-way bank conflict, which costs less than the selects that avoid it: the
 // kernel is short of issue slots, not of shared-memory bandwidth).
+// `own`, when given, holds the thread's own states of row `in` (what it computed a timestep ago),
+// which saves reading them back.
 template <class Topo, int SPT>
 __device__ __forceinline__ void thread_terms(const float *in, const unsigned char *row, int j, int k0,
-                                             float stay, float (&v)[SPT][5]) {
+                                             float stay, float (&v)[SPT][5], const float *own = nullptr) {
     const unsigned char *piece = row + 32 * j;
     const uint4 lo = *reinterpret_cast<const uint4 *>(piece);
     const uint4 hi = *reinterpret_cast<const uint4 *>(piece + 16);
@@ -127,7 +129,7 @@ __device__ __forceinline__ void thread_terms(const float *in, const unsigned cha
     const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
 #pragma unroll
     for (int k = 0; k < SPT; ++k) {
-        v[k][0] = in[Topo::state(j, k0 + k)] + stay;
+        v[k][0] = (own ? own[k] : in[Topo::state(j, k0 + k)]) + stay;
 #pragma unroll
         for (int b = 0; b < 4; ++b) v[k][b + 1] = x[b] + Topo::template score<SPT>(w, k0, k, b);
     }
@@ -554,12 +556,13 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
     }
     __syncthreads();
     const uint32_t lt_mask = (1u << lane) - 1u;
+    float res[SPT];  // the thread's states of the current row: its stay terms for the next timestep
+#pragma unroll
+    for (int k = 0; k < SPT; ++k) res[k] = 0.f;
     for (int i = 0; i < T; ++i) {
-        float v[SPT][5], res[SPT];
+        float v[SPT][5];
         bool ok[SPT];
-        // (the stay term is read from the row, not kept in a register: the checker may have
-        // corrected it)
-        thread_terms<Topo, SPT>(sm.alpha[i % 3], sm.ring[i % RING], j, k0, stay, v);
+        thread_terms<Topo, SPT>(sm.alpha[i % 3], sm.ring[i % RING], j, k0, stay, v, res);
         ofd::lse5_fast_guess<SPT>(v, res, ok);
         uint32_t bad[SPT];
         int total = 0;
@@ -615,7 +618,11 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
         if (lane == 0) sm.n_listed[i & 1][warp] = total;
         thread_store<Topo, SPT>(sm.alpha[(i + 1) % 3], out_chunk + (size_t)Topo::out_row(i, T) * NS, j, k0, res, !POST);
         __syncthreads();
-        if (sm.n_wrong[i & 1]) __syncthreads();  // the checker is correcting this row's readers
+        if (sm.n_wrong[i & 1]) {
+            __syncthreads();  // the checker is correcting this row's readers
+#pragma unroll
+            for (int k = 0; k < SPT; ++k) res[k] = sm.alpha[(i + 1) % 3][Topo::state(j, k0 + k)];  // maybe corrected
+        }
     }
     if (POST) __syncthreads();  // the last row is final
 }
