@@ -559,10 +559,16 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
     float res[SPT];  // the thread's states of the current row: its stay terms for the next timestep
 #pragma unroll
     for (int k = 0; k < SPT; ++k) res[k] = 0.f;
+    // rotating pointers instead of i % 3 and i % RING: row i is read from `in`, row i+1 goes to `nxt`
+    const float *in = sm.alpha[0];
+    float *nxt = sm.alpha[1], *spare = sm.alpha[2];
+    const unsigned char *row = sm.ring[0];
+    float *gmem_out = out_chunk + (size_t)Topo::out_row(0, T) * NS;
+    const ptrdiff_t gmem_step = Topo::kForward ? (ptrdiff_t)NS : -(ptrdiff_t)NS;
     for (int i = 0; i < T; ++i) {
         float v[SPT][5];
         bool ok[SPT];
-        thread_terms<Topo, SPT>(sm.alpha[i % 3], sm.ring[i % RING], j, k0, stay, v, res);
+        thread_terms<Topo, SPT>(in, row, j, k0, stay, v, res);
         ofd::lse5_fast_guess<SPT>(v, res, ok);
         uint32_t bad[SPT];
         int total = 0;
@@ -598,7 +604,7 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
                 const int e = first + lane;
                 const int st = sm.redo_state[warp][e < total ? e : 0];
                 float w[5];
-                terms_of<Topo>(st, sm.alpha[i % 3], sm.ring[i % RING], stay, w);
+                terms_of<Topo>(st, in, row, stay, w);
                 const float x = ofx::lse5_exact(w, tr);
                 if (e < total) sm.redo_value[warp][e] = x;
             }
@@ -616,13 +622,19 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
             }
         }
         if (lane == 0) sm.n_listed[i & 1][warp] = total;
-        thread_store<Topo, SPT>(sm.alpha[(i + 1) % 3], out_chunk + (size_t)Topo::out_row(i, T) * NS, j, k0, res, !POST);
+        thread_store<Topo, SPT>(nxt, gmem_out, j, k0, res, !POST);
         __syncthreads();
         if (sm.n_wrong[i & 1]) {
             __syncthreads();  // the checker is correcting this row's readers
 #pragma unroll
-            for (int k = 0; k < SPT; ++k) res[k] = sm.alpha[(i + 1) % 3][Topo::state(j, k0 + k)];  // maybe corrected
+            for (int k = 0; k < SPT; ++k) res[k] = nxt[Topo::state(j, k0 + k)];  // maybe corrected
         }
+        float *const was_in = const_cast<float *>(in);
+        in = nxt;
+        nxt = spare;
+        spare = was_in;
+        row = (row == sm.ring[RING - 1]) ? sm.ring[0] : row + Smem::kRowBytes;
+        gmem_out += gmem_step;
     }
     if (POST) __syncthreads();  // the last row is final
 }
@@ -644,7 +656,7 @@ scan_kernel(const __half *__restrict__ scores, float *__restrict__ bwd, float *_
 }
 
 template <int NS, int SPT, int RING>
-__global__ void __launch_bounds__(NS / SPT + 64)
+__global__ void __launch_bounds__(NS / SPT + 64, (NS <= 256 ? 5 : 2))
 scan_spec_kernel(const __half *__restrict__ scores, float *__restrict__ bwd, float *__restrict__ fwd,
                  int T, int N, int n_bwd_blocks, float stay, const ofx::Tables *__restrict__ tables,
                  int *status) {
