@@ -389,7 +389,7 @@ def main():
             "dtype": "f32 storage, f64 inside the log-sum-exp, fp16 scores", "data": "synthetic",
             "config": CONFIG, "chunks_total": total_chunks,
             "timing": "CUDA events recorded by the library on its own stream, summed over steps, max over ranks",
-            "bases_per_sec": bases / dev_s * 1.0,
+            "bases_per_sec": bases * args.steps / dev_s,
             "wall_ms_per_step": 1e3 * wall_s / args.steps,
             "kernel_ms": {k: per[k] for k in ("bwd_scan", "fwd_scan", "beam_search", "posterior_seq", "d2h")},
             "kernel_overlap": "fwd_scan (forward scan + posterior) runs on a second stream beside beam_search; the others are sequential",
