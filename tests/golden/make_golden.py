@@ -1,7 +1,8 @@
 """Generates the committed golden fixtures from the UNMODIFIED reference.
 
-Run in a container that has the reference checkout (default /root/reference) and the built
-reference library (make -C oracle ref):
+Run where the reference checkout is present (its location is taken from the environment variable
+OPENFISH_REF, else the oracle Makefile's default) and the reference library has been built
+(make -C oracle ref):
 
     python tests/golden/make_golden.py
 
