@@ -398,7 +398,8 @@ def main():
                          "frac": achieved / peak, "traffic": ncu_traffic(dom), "peak_source": peak_src,
                          "algorithmic_bytes_per_launch": dom_bytes},
             "roofline_whole_decode": {"achieved": whole, "peak": peak, "unit": "GB/s", "frac": whole / peak,
-                                      "algorithmic_bytes_per_chunk": B_CHUNK},
+                                      "algorithmic_bytes_per_chunk": B_CHUNK,
+                                      "frac_of_nominal_8000_gbs": whole / 8000.0},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(scores.numel() * 2),
                     "d2h_bytes_per_step": int(3 * n_local * T), "steps": e2e_steps,
                     "call": "openfish_decode_gpu after a page-locked host-to-device copy of the scores; "
