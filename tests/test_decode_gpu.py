@@ -56,7 +56,8 @@ def test_sup_T1666(native_lib, oracle_mod):
 
 
 @pytest.mark.parametrize("sl,T,N", [(3, 1, 1), (3, 2, 3), (3, 7, 5), (4, 9, 1), (3, 257, 7), (4, 513, 3),
-                                    (5, 3, 2), (3, 300, 9)])
+                                    (5, 3, 2), (3, 300, 9), (4, 1, 1), (4, 2, 2), (5, 1, 1), (5, 2, 1),
+                                    (4, 33, 2), (5, 65, 1)])
 def test_ragged_shapes(native_lib, oracle_mod, sl, T, N):
     from openfish_b200 import synth
     check(native_lib, oracle_mod, synth.make_scores(T, N, sl, 40 + T + N), sl, min_identical=1.0)
