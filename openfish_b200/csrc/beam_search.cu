@@ -29,6 +29,12 @@
 namespace {
 
 constexpr int kBeam = 32;
+// Threads per block: the beam warp, the copy warp and a padding warp that exits at once.  With
+// two-warp blocks the warp slots of an SM fill in pairs and every beam warp lands on the same two
+// of the four schedulers, where they queue behind each other; a block of three warps rotates them
+// over all four (measured on the hac decode: 3.87 -> 3.58 ms; fast, with seven blocks per SM:
+// 4.84 -> 4.39 ms).
+constexpr int kBeamBlock = 96;
 
 
 // Warp maximum of a float through the sm_100a float reduction instruction.
@@ -98,11 +104,11 @@ struct BeamSmem {
 };
 
 template <int NS, int RING>
-__global__ void __launch_bounds__(64)
+__global__ void __launch_bounds__(kBeamBlock)
 beam_search_kernel(const OfDecodeArgs a) {
     constexpr int BITS = (NS == 64) ? 6 : (NS == 256 ? 8 : 10);
     constexpr int MSB = NS / 4;
-    constexpr int NT = 64;
+    constexpr int NT = kBeamBlock;
     using Smem = BeamSmem<NS, RING>;
     extern __shared__ unsigned char smem_raw[];
     Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
@@ -132,6 +138,7 @@ beam_search_kernel(const OfDecodeArgs a) {
     const float *bwd_chunk = a.bwd + (size_t)chunk * (size_t)(T + 1) * NS;
     unsigned char *bp_chunk = a.bp + (size_t)chunk * (size_t)(T + 1) * kBeam;
 
+    if (warp >= 2) return;  // the padding warp: it has helped to set shared memory up, that is all
     if (warp == 1) {
         // ------------------------------------------------------------------ copy warp
         if (lane == 0) {
@@ -424,7 +431,7 @@ cudaError_t launch_beam(const OfDecodeArgs &a, cudaStream_t stream) {
     auto kern = beam_search_kernel<NS, RING>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
     if (e != cudaSuccess) return e;
-    kern<<<a.N, 64, bytes, stream>>>(a);
+    kern<<<a.N, kBeamBlock, bytes, stream>>>(a);
     return cudaGetLastError();
 }
 
