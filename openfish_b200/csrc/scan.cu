@@ -656,7 +656,7 @@ scan_kernel(const __half *__restrict__ scores, float *__restrict__ bwd, float *_
 }
 
 template <int NS, int SPT, int RING>
-__global__ void __launch_bounds__(NS / SPT + 64, (NS <= 256 ? 5 : 2))
+__global__ void __launch_bounds__(NS / SPT + 64, (NS <= 256 ? 4 : 2))
 scan_spec_kernel(const __half *__restrict__ scores, float *__restrict__ bwd, float *__restrict__ fwd,
                  int T, int N, int n_bwd_blocks, float stay, const ofx::Tables *__restrict__ tables,
                  int *status) {
