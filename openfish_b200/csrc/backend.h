@@ -18,11 +18,18 @@ int ofb_gpubuf_destroy(openfish_gpubuf_t *gpubuf);
 /* Checks that gpubuf came from ofb_gpubuf_create with this shape. */
 int ofb_gpubuf_check(const openfish_gpubuf_t *gpubuf, int T, int N, int state_len);
 
+/* What a decode takes from openfish_opt_t, plus where to run it. */
+typedef struct {
+    float beam_cut, blank_score, q_shift, q_scale;
+    float score_scale;   /* options->temperature: the beam search's score_scale (src/beam_search.c:233) */
+    int on_caller_stream;/* 0: order after the legacy default stream (the reference's behaviour) */
+    void *caller_stream; /* cudaStream_t the scores were produced on, when on_caller_stream */
+} ofb_decode_params_t;
+
 /* Enqueue one decode and the copies of moves/sequence/qstring into the three host buffers. */
-int ofb_decode_submit(int T, int N, int C, const void *scores, int state_len, float beam_cut,
-                      float blank_score, float q_shift, float q_scale,
-                      const openfish_gpubuf_t *gpubuf, uint8_t *moves, char *sequence,
-                      char *qstring);
+int ofb_decode_submit(int T, int N, int C, const void *scores, int state_len,
+                      const ofb_decode_params_t *params, const openfish_gpubuf_t *gpubuf,
+                      uint8_t *moves, char *sequence, char *qstring);
 /* Wait for the gpubuf's decode in flight; returns its status (device-side status included). */
 int ofb_decode_wait(const openfish_gpubuf_t *gpubuf);
 int ofb_last_decode_ms(const openfish_gpubuf_t *gpubuf, float ms[8]);

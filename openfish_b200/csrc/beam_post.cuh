@@ -25,6 +25,7 @@ struct OfDecodeArgs {
     int *status;
     int T, N, C, state_len;
     float stay, log_beam_cut, q_shift, q_scale;
+    float score_scale;         // multiplies every transition score in the beam search (src/beam_search.c:233)
 };
 
 // needs scores, bwd; writes bp, init_kmers

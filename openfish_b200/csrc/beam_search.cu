@@ -230,8 +230,9 @@ beam_search_kernel(const OfDecodeArgs a) {
             // their candidates are voided afterwards
             const float4 bw = *reinterpret_cast<const float4 *>(brow + 4 * q);
             const __half *sp = srow + 16 * q + top;
-            const float x0 = __half2float(sp[0]), x1 = __half2float(sp[4]);
-            const float x2 = __half2float(sp[8]), x3 = __half2float(sp[12]);
+            // (float)score * score_scale, rounded before it is added (src/beam_search.c:233-234)
+            const float x0 = __fmul_rn(__half2float(sp[0]), a.score_scale), x1 = __fmul_rn(__half2float(sp[4]), a.score_scale);
+            const float x2 = __fmul_rn(__half2float(sp[8]), a.score_scale), x3 = __fmul_rn(__half2float(sp[12]), a.score_scale);
             const float bs = brow[state];
             c0 = __fadd_rn(__fadd_rn(score, x0), bw.x);
             c1 = __fadd_rn(__fadd_rn(score, x1), bw.y);

@@ -189,10 +189,11 @@ extern "C" int ofb_gpubuf_check(const openfish_gpubuf_t *gpubuf, int T, int N, i
 }
 
 extern "C" int ofb_decode_submit(int T, int N, int C, const void *scores, int state_len,
-                                 float beam_cut, float blank_score, float q_shift, float q_scale,
-                                 const openfish_gpubuf_t *gpubuf, uint8_t *moves, char *sequence,
-                                 char *qstring) {
+                                 const ofb_decode_params_t *params, const openfish_gpubuf_t *gpubuf,
+                                 uint8_t *moves, char *sequence, char *qstring) {
     GpuBuf *g = priv(gpubuf);
+    const float beam_cut = params->beam_cut, blank_score = params->blank_score;
+    const float q_shift = params->q_shift, q_scale = params->q_scale;
     if (g->pending) return fail(OPENFISH_B200_ERR_ARGUMENT, "a decode is already in flight on this gpubuf");
     int dev = -1;
     CU(cudaGetDevice(&dev));
@@ -220,6 +221,7 @@ extern "C" int ofb_decode_submit(int T, int N, int C, const void *scores, int st
     a.log_beam_cut = beam_cut > 0.0f ? logf(beam_cut) : 3.402823466e+38f;  // src/beam_search.c:135
     a.q_shift = q_shift;
     a.q_scale = q_scale;
+    a.score_scale = params->score_scale;
 
     // stream:  backward scan -> beam search ----------------------> posterior + sequence -> copies
     // stream2:                  forward scan (beside the beam search) --^

@@ -89,7 +89,7 @@ extern "C" int openfish_b200_decode_static(int T, int N, int C, const void *scor
         return report(OPENFISH_B200_ERR_ARGUMENT, "need T >= 1, N >= 1 and state_len 3, 4 or 5");
     if (T > 16384) return report(OPENFISH_B200_ERR_TOO_LONG, "T exceeds 16384 timesteps");
     const size_t ns = (size_t)1 << (2 * state_len);
-    if ((size_t)C < 4 * ns || C % 8 != 0 || ((size_t)scores_TNC & 15u))
+    if (C < 0 || (size_t)C < 4 * ns || C % 8 != 0 || ((size_t)scores_TNC & 15u))
         return report(OPENFISH_B200_ERR_LAYOUT,
                       "C must be a multiple of 8 and at least 4*4^state_len, scores 16-byte aligned");
     if (options->beam_width != 32)
@@ -156,6 +156,7 @@ extern "C" int openfish_b200_decode_static(int T, int N, int C, const void *scor
         a.log_beam_cut = options->beam_cut > 0.0f ? logf(options->beam_cut) : 3.402823466e+38f;
         a.q_shift = options->q_shift;
         a.q_scale = options->q_scale;
+        a.score_scale = options->temperature;
         e = of_launch_beam_search(a, stream);
         if (e == cudaSuccess) e = of_launch_posterior_seq(a, stream);
     }

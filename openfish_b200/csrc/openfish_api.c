@@ -124,9 +124,10 @@ void openfish_b200_decode_submit(int T, int N, int C, const void *scores_TNC, in
     }
     if (check_decode_args(__func__, T, N, C, scores_TNC, state_len, options, gpubuf)) return;
     trace(__func__, "scores tensor dim: %d, %d, %d", T, N, C);
-    backend_failed(__func__, ofb_decode_submit(T, N, C, scores_TNC, state_len, options->beam_cut,
-                                               options->blank_score, options->q_shift,
-                                               options->q_scale, gpubuf, moves, sequence, qstring));
+    const ofb_decode_params_t params = {options->beam_cut, options->blank_score, options->q_shift,
+                                        options->q_scale, options->temperature, 0, NULL};
+    backend_failed(__func__, ofb_decode_submit(T, N, C, scores_TNC, state_len, &params, gpubuf, moves,
+                                               sequence, qstring));
 }
 
 void openfish_b200_decode_wait(const openfish_gpubuf_t *gpubuf) {

@@ -57,6 +57,8 @@ def _oracle():
         lib.oracle_decode.restype = C.c_int
         lib.oracle_decode.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, _fp, C.c_int,
                                       C.POINTER(Opt), _u8, _u8, _u8, _fp, _fp, _fp, _fp, _fp, _fp]
+        lib.oracle_decode_ex.restype = C.c_int
+        lib.oracle_decode_ex.argtypes = lib.oracle_decode.argtypes + [_i32, C.c_int]
         lib.oracle_rotary_emb.restype = None
         lib.oracle_rotary_emb.argtypes = [_fp, _fp, _fp, C.c_int, C.c_int, C.c_int, C.c_int,
                                           C.c_long, C.c_long, C.c_long]
@@ -89,6 +91,14 @@ def _ref():
         lib.ref_beam_search.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_int,
                                         C.c_int, C.c_float, C.c_float, C.c_void_p, C.c_void_p,
                                         C.c_void_p, C.c_void_p]
+        lib.ref_beam_search_scaled.restype = None
+        lib.ref_beam_search_scaled.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_int,
+                                               C.c_int, C.c_float, C.c_float, C.c_void_p, C.c_void_p,
+                                               C.c_void_p, C.c_float, C.c_float, C.c_void_p]
+        lib.ref_generate_sequence.restype = None
+        lib.ref_generate_sequence.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_float,
+                                              C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p,
+                                              C.c_void_p, C.c_void_p]
         lib.openfish_rotary_emb_cpu.restype = None
         lib.openfish_rotary_emb_cpu.argtypes = [C.c_void_p] * 3 + [C.c_int] * 9
         _libs["r"] = lib
@@ -117,33 +127,41 @@ def backward_scan(scores, state_len):
     return out
 
 
-def decode(scores, state_len, opt=None, nthreads=1, tensors=False):
+SCAN_STAY_FROM_OPTIONS = 1      # scans use opt.blank_score, as the reference's CUDA launcher does
+TEMPERATURE_SCALES_SCORES = 2   # the beam search's score_scale = opt.temperature
+
+
+def decode(scores, state_len, opt=None, nthreads=1, tensors=False, flags=0):
     """Restatement decode.  scores: float32 [T][N][C] (fp16 values widened).
 
     Returns dict(moves, sequence, qstring: uint8 [N][T]) plus, with tensors=True, bwd, fwdbwd,
-    post [N][T+1][ns], qual [N][T][4], base_probs, total_probs [N][T]."""
+    post [N][T+1][ns], qual [N][T][4], base_probs, total_probs [N][T] and states int32 [N][T]
+    (the base of the path at every timestep).  flags = 0 is the reference CPU decoder's
+    behaviour; SCAN_STAY_FROM_OPTIONS and TEMPERATURE_SCALES_SCORES switch on the two places
+    where the options reach further than in that decoder."""
     scores = np.ascontiguousarray(scores, dtype=np.float32)
     T, N, Cc = scores.shape
     ns = 4 ** state_len
     opt = opt or decoder_init()
     out = {k: np.zeros((N, T), np.uint8) for k in ("moves", "sequence", "qstring")}
+    lib = _oracle()
     if tensors:
         for k in ("bwd", "fwdbwd", "post"):
             out[k] = np.zeros((N, T + 1, ns), np.float32)
         out["qual"] = np.zeros((N, T, 4), np.float32)
         out["base_probs"] = np.zeros((N, T), np.float32)
         out["total_probs"] = np.zeros((N, T), np.float32)
-        extra = [out[k] for k in ("bwd", "fwdbwd", "post", "qual", "base_probs", "total_probs")]
-        rc = _oracle().oracle_decode(T, N, Cc, nthreads, scores, state_len, C.byref(opt),
-                                     out["moves"], out["sequence"], out["qstring"], *extra)
+        out["states"] = np.zeros((N, T), np.int32)
+        extra = [out[k] for k in ("bwd", "fwdbwd", "post", "qual", "base_probs", "total_probs", "states")]
+        rc = lib.oracle_decode_ex(T, N, Cc, nthreads, scores, state_len, C.byref(opt),
+                                  out["moves"], out["sequence"], out["qstring"], *extra, flags)
     else:
-        lib = _oracle()
-        fn = lib.oracle_decode
+        fn = lib.oracle_decode_ex
         saved = fn.argtypes
-        fn.argtypes = saved[:10] + [C.c_void_p] * 6
+        fn.argtypes = saved[:10] + [C.c_void_p] * 7 + [C.c_int]
         try:
             rc = fn(T, N, Cc, nthreads, scores, state_len, C.byref(opt), out["moves"],
-                    out["sequence"], out["qstring"], None, None, None, None, None, None)
+                    out["sequence"], out["qstring"], None, None, None, None, None, None, None, flags)
         finally:
             fn.argtypes = saved
     if rc != 0:
@@ -164,6 +182,40 @@ def ref_decode(scores, state_len, opt=None, nthreads=1):
     for k, p in (("moves", m), ("sequence", s), ("qstring", q)):
         out[k] = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint8)), shape=(N, T)).copy()
         _libs["libc"].free(C.cast(p, C.c_void_p))
+    return out
+
+
+def ref_decode_tensors(scores, state_len, opt=None, score_scale=1.0, posts_scale=1.0):
+    """The reference's decode put together from its own routines one chunk at a time, the way
+    src/decode_cpu.c:188-229 does, but keeping every intermediate and with beam_search_cpu's two
+    scale arguments open (the reference's decoder passes 1.0f for both): backward_scan,
+    forward_scan, softmax, beam_search_cpu, generate_sequence_cpu.  Returns the same keys as
+    decode(tensors=True)."""
+    lib = _ref()
+    scores = np.ascontiguousarray(scores, dtype=np.float32)
+    T, N, Cc = scores.shape
+    ns = 4 ** state_len
+    opt = opt or decoder_init()
+    out = ref_scan_tensors(scores, state_len)
+    out.update({k: np.zeros((N, T), np.uint8) for k in ("moves", "sequence", "qstring")})
+    out["states"] = np.zeros((N, T), np.int32)
+    out["qual"] = np.zeros((N, T, 4), np.float32)
+    out["base_probs"] = np.zeros((N, T), np.float32)
+    out["total_probs"] = np.zeros((N, T), np.float32)
+    beam_vector = np.zeros(32 * (T + 1) * 8, np.uint8)
+    flat = scores.reshape(-1)
+    for c in range(N):
+        chunk_scores = flat[c * ns * 4:]
+        lib.ref_beam_search_scaled(chunk_scores.ctypes.data, N * Cc, out["bwd"][c].ctypes.data,
+                                   out["post"][c].ctypes.data, 2 * state_len, T, opt.beam_cut,
+                                   opt.blank_score, out["states"][c].ctypes.data,
+                                   out["moves"][c].ctypes.data, out["qual"][c].ctypes.data,
+                                   score_scale, posts_scale, beam_vector.ctypes.data)
+        lib.ref_generate_sequence(out["moves"][c].ctypes.data, out["states"][c].ctypes.data,
+                                  out["qual"][c].ctypes.data, opt.q_shift, opt.q_scale, T,
+                                  int(out["moves"][c].sum()), out["base_probs"][c].ctypes.data,
+                                  out["total_probs"][c].ctypes.data, out["sequence"][c].ctypes.data,
+                                  out["qstring"][c].ctypes.data)
     return out
 
 

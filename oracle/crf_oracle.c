@@ -43,7 +43,7 @@ typedef struct {
     float blank_score;
     float q_shift;
     float q_scale;
-    float temperature; /* ignored (src/decode_cpu.c:216 passes 1.0f) */
+    float temperature; /* ignored by oracle_decode (src/decode_cpu.c:216 passes 1.0f); see oracle_decode_ex */
     uint8_t move_pad;  /* ignored */
 } oracle_opt_t;
 
@@ -63,9 +63,11 @@ static float lse5(const float v[5]) {
 
 /* Backward scores of one chunk.  src/decode_cpu.c:13-52.  Row T is zero; row t is built from
  * row t+1.  State s can stay (fixed score 2.0f, :14) or move to u = (4s mod ns) + b; that
- * transition's score sits at column 4u + (4s div ns) of timestep t (:33-35,41-42). */
-void oracle_backward_scan(const float *scores, float *bwd, int chunk, int T, int N, int ns) {
-    const float stay = 2.0f;
+ * transition's score sits at column 4u + (4s div ns) of timestep t (:33-35,41-42).
+ * The _stay variants take the stay score as an argument: the reference's CUDA launcher hands
+ * its scans options->blank_score (src/decode_cuda.cu:115) where the CPU scans hard-code 2.0f. */
+void oracle_backward_scan_stay(const float *scores, float *bwd, int chunk, int T, int N, int ns,
+                               float stay) {
     const size_t row = (size_t)ns * OR_BASES;
     const float *cs = scores + (size_t)chunk * row;
     float *out = bwd + (size_t)chunk * (T + 1) * ns;
@@ -84,14 +86,16 @@ void oracle_backward_scan(const float *scores, float *bwd, int chunk, int T, int
         }
     }
 }
+void oracle_backward_scan(const float *scores, float *bwd, int chunk, int T, int N, int ns) {
+    oracle_backward_scan_stay(scores, bwd, chunk, T, N, ns, 2.0f);
+}
 
 /* Forward scan of one chunk fused with the fwd+bwd sum.  src/decode_cpu.c:54-119.  It runs
  * T+1 steps; step t writes out[t][s] = fwd[t][s] + bwd[t][s] (float add, :115-116) and builds
  * fwd[t+1]; scores at step T count as zero (:99).  Predecessors of s are (s div 4) + b*ns/4
  * with score column 4s + b (:91-92,101). */
-void oracle_forward_scan(const float *scores, const float *bwd, float *fwdbwd, int chunk, int T,
-                         int N, int ns) {
-    const float stay = 2.0f;
+void oracle_forward_scan_stay(const float *scores, const float *bwd, float *fwdbwd, int chunk, int T,
+                              int N, int ns, float stay) {
     const int msb = ns / OR_BASES;
     const size_t row = (size_t)ns * OR_BASES;
     const float *cs = scores + (size_t)chunk * row;
@@ -113,6 +117,10 @@ void oracle_forward_scan(const float *scores, const float *bwd, float *fwdbwd, i
             fwdbwd[base + s] = in[s] + bwd[base + s];
         }
     }
+}
+void oracle_forward_scan(const float *scores, const float *bwd, float *fwdbwd, int chunk, int T,
+                         int N, int ns) {
+    oracle_forward_scan_stay(scores, bwd, fwdbwd, chunk, T, N, ns, 2.0f);
 }
 
 /* Posterior = softmax over states of fwd+bwd, row by row.  src/decode_cpu.c:121-147: float
@@ -180,11 +188,14 @@ static size_t count_at_least(const float *v, size_t n, float cut) {
 
 /* One chunk of beam search + traceback + per-timestep quality.  src/beam_search.c:117-497.
  * bp receives one {state, prev, stay} triple per kept element and timestep, laid out
- * [T+1][32] like the reference's beam_vector. */
+ * [T+1][32] like the reference's beam_vector.  score_scale multiplies every transition score
+ * (:233) and posts_scale every posterior (:452,483); the reference's decoder passes 1.0f for
+ * both (src/decode_cpu.c:216).  On return states[t] is the base (k-mer mod 4) of the path at
+ * timestep t, as the reference leaves it (:446). */
 void oracle_beam_search(const float *scores, size_t t_stride, const float *bwd, const float *post,
                         int state_bits, int T, float beam_cut, float stay_score, int32_t *states,
                         uint8_t *moves, float *qual, int32_t *bp_state, uint8_t *bp_prev,
-                        uint8_t *bp_stay) {
+                        uint8_t *bp_stay, float score_scale, float posts_scale) {
     const int ns = 1 << state_bits;
     const int32_t mask = ns - 1;
     const float log_cut = beam_cut > 0.0f ? logf(beam_cut) : FLT_MAX; /* :135 */
@@ -227,7 +238,7 @@ void oracle_beam_search(const float *scores, size_t t_stride, const float *bwd, 
             for (int b = 0; b < OR_BASES; ++b) {
                 const int32_t ns_ = ((p_state[i] << 2) & mask) | b;
                 const int32_t col = (ns_ << 2) + ((p_state[i] << 2) >> state_bits);
-                const float x = sc[col] * 1.0f;
+                const float x = sc[col] * score_scale; /* :233 */
                 const float v = p_score[i] + x + back[ns_];
                 c_hash[n] = oracle_crc32c(p_hash[i], (uint32_t)b, 2);
                 c_state[n] = ns_;
@@ -351,7 +362,7 @@ void oracle_beam_search(const float *scores, size_t t_stride, const float *bwd, 
         const int base = st % OR_BASES;
         states[t] = base;
         const float *p = post + ((size_t)(t + 1) << state_bits);
-        float prob = p[st] * 1.0f;
+        float prob = p[st] * posts_scale; /* :452 */
         int nb[8];
         for (int b = 0; b < OR_BASES; ++b) {
             nb[2 * b] = (st >> 2) + msb * b;
@@ -360,7 +371,7 @@ void oracle_beam_search(const float *scores, size_t t_stride, const float *bwd, 
         for (int k = 0; k < 8; ++k) {
             int fresh = nb[k] != st;
             for (int m = 0; fresh && m < k; ++m) fresh = nb[m] != nb[k];
-            if (fresh) prob += p[nb[k]] * 1.0f;
+            if (fresh) prob += p[nb[k]] * posts_scale; /* :483 */
         }
         if (prob > 1.0f) prob = 1.0f;
         else if (prob < 0.0f) prob = 0.0f;
@@ -408,6 +419,7 @@ void oracle_generate_sequence(const uint8_t *moves, const int32_t *bases, const 
 typedef struct {
     const float *scores;
     int T, N, C, state_len, lo, hi;
+    float scan_stay, score_scale;
     const oracle_opt_t *opt;
     float *bwd, *fwdbwd, *post, *qual, *base_probs, *total_probs;
     int32_t *states, *bp_state;
@@ -421,8 +433,8 @@ static void *run_range(void *arg) {
     const int ns = 1 << bits;
     const int T = j->T;
     for (int c = j->lo; c < j->hi; ++c) {
-        oracle_backward_scan(j->scores, j->bwd, c, T, j->N, ns);
-        oracle_forward_scan(j->scores, j->bwd, j->fwdbwd, c, T, j->N, ns);
+        oracle_backward_scan_stay(j->scores, j->bwd, c, T, j->N, ns, j->scan_stay);
+        oracle_forward_scan_stay(j->scores, j->bwd, j->fwdbwd, c, T, j->N, ns, j->scan_stay);
         oracle_softmax(j->fwdbwd, j->post, c, T, ns);
         const size_t cs = (size_t)c * ns * (T + 1);
         const size_t bo = (size_t)c * OR_BEAM * (T + 1);
@@ -430,7 +442,7 @@ static void *run_range(void *arg) {
                            j->post + cs, bits, T, j->opt->beam_cut, j->opt->blank_score,
                            j->states + (size_t)c * T, j->moves + (size_t)c * T,
                            j->qual + (size_t)c * T * OR_BASES, j->bp_state + bo, j->bp_prev + bo,
-                           j->bp_stay + bo);
+                           j->bp_stay + bo, j->score_scale, 1.0f);
         oracle_generate_sequence(j->moves + (size_t)c * T, j->states + (size_t)c * T,
                                  j->qual + (size_t)c * T * OR_BASES, j->opt->q_shift,
                                  j->opt->q_scale, T, j->base_probs + (size_t)c * T,
@@ -444,10 +456,16 @@ static void *run_range(void *arg) {
  * callocs them, src/decode_cpu.c:252-259).  The tensor outputs (bwd, fwdbwd, post:
  * N*(T+1)*ns floats; qual: N*T*4; base_probs,total_probs: N*T) may each be NULL, in which case
  * scratch is allocated and dropped.  Returns 0, or -1 on allocation failure. */
-int oracle_decode(int T, int N, int C, int nthreads, const float *scores, int state_len,
-                  const oracle_opt_t *opt, uint8_t *moves, char *sequence, char *qstring,
-                  float *bwd, float *fwdbwd, float *post, float *qual, float *base_probs,
-                  float *total_probs) {
+/* flags for oracle_decode_ex */
+#define OR_FLAG_SCAN_STAY_FROM_OPTIONS 1 /* scans use opt->blank_score, as src/decode_cuda.cu:115 does */
+#define OR_FLAG_TEMPERATURE_SCALES_SCORES 2 /* beam search's score_scale (:233) = opt->temperature */
+
+/* states_out (may be NULL): N*T int32, the base of the decoded path at every timestep, i.e. the
+ * contents of the reference's `states` buffer after beam_search_cpu (src/beam_search.c:446). */
+int oracle_decode_ex(int T, int N, int C, int nthreads, const float *scores, int state_len,
+                     const oracle_opt_t *opt, uint8_t *moves, char *sequence, char *qstring,
+                     float *bwd, float *fwdbwd, float *post, float *qual, float *base_probs,
+                     float *total_probs, int32_t *states_out, int flags) {
     const int ns = 1 << (2 * state_len);
     const size_t tens = (size_t)N * (T + 1) * ns;
     float *own[6] = {0};
@@ -476,7 +494,9 @@ int oracle_decode(int T, int N, int C, int nthreads, const float *scores, int st
         const int each = N / nthreads, extra = N % nthreads;
         int lo = 0;
         for (int k = 0; k < nthreads; ++k) {
-            job_t j = {scores, T, N, C, state_len, lo, lo + each + (k < extra), opt,
+            job_t j = {scores, T, N, C, state_len, lo, lo + each + (k < extra),
+                       (flags & OR_FLAG_SCAN_STAY_FROM_OPTIONS) ? opt->blank_score : 2.0f,
+                       (flags & OR_FLAG_TEMPERATURE_SCALES_SCORES) ? opt->temperature : 1.0f, opt,
                        bwd, fwdbwd, post, qual, base_probs, total_probs,
                        states, bp_state, moves, bp_prev, bp_stay, sequence, qstring};
             lo = j.hi;
@@ -487,12 +507,22 @@ int oracle_decode(int T, int N, int C, int nthreads, const float *scores, int st
         free(tid);
         free(jobs);
     }
+    if (rc == 0 && states_out) memcpy(states_out, states, sizeof(int32_t) * N * T);
     free(states);
     free(bp_state);
     free(bp_prev);
     free(bp_stay);
     for (int i = 0; i < 6; ++i) free(own[i]);
     return rc;
+}
+
+/* The reference decoder's behaviour: stay score 2.0f in the scans, temperature ignored. */
+int oracle_decode(int T, int N, int C, int nthreads, const float *scores, int state_len,
+                  const oracle_opt_t *opt, uint8_t *moves, char *sequence, char *qstring,
+                  float *bwd, float *fwdbwd, float *post, float *qual, float *base_probs,
+                  float *total_probs) {
+    return oracle_decode_ex(T, N, C, nthreads, scores, state_len, opt, moves, sequence, qstring, bwd,
+                            fwdbwd, post, qual, base_probs, total_probs, NULL, 0);
 }
 
 /* ---------------------------------------------------------------------------------------- */

@@ -28,3 +28,24 @@ void ref_beam_search(const float *scores, size_t t_stride, const float *bwd, con
     beam_search_cpu(scores, t_stride, bwd, post, state_bits, T, beam_cut, stay_score, states, moves,
                     qual, 1.0f, 1.0f, (beam_element_t *)beam_vector);
 }
+
+/* The same with the reference's two scale arguments exposed (src/beam_search.c:129-130: score_scale
+ * multiplies every transition score, :233; posts_scale every posterior, :452,483), which its own
+ * decoder always passes as 1.0f (src/decode_cpu.c:216). */
+void ref_beam_search_scaled(const float *scores, size_t t_stride, const float *bwd, const float *post,
+                            int state_bits, int T, float beam_cut, float stay_score, int32_t *states,
+                            uint8_t *moves, float *qual, float score_scale, float posts_scale,
+                            void *beam_vector) {
+    beam_search_cpu(scores, t_stride, bwd, post, state_bits, T, beam_cut, stay_score, states, moves,
+                    qual, score_scale, posts_scale, (beam_element_t *)beam_vector);
+}
+
+/* Sequence and quality string of one chunk through the reference's generate_sequence_cpu
+ * (src/beam_search.c:49-99); base_probs and total_probs must arrive zeroed, as the reference's
+ * decoder hands them over (src/decode_cpu.c:218-223). */
+void ref_generate_sequence(const uint8_t *moves, const int32_t *states, const float *qual, float shift,
+                           float scale, size_t T, size_t seq_len, float *base_probs, float *total_probs,
+                           char *sequence, char *qstring) {
+    generate_sequence_cpu(moves, states, qual, shift, scale, T, seq_len, base_probs, total_probs,
+                          sequence, qstring);
+}

@@ -44,4 +44,7 @@ def load_golden(name):
     return d
 
 
-SYNTH_CASES = ["fast", "hac", "sup", "fast_c320", "fast_stays", "hac_cut10"]
+SYNTH_CASES = ["fast", "hac", "sup", "fast_c320", "fast_stays", "hac_cut10", "fast_temp07", "hac_temp16"]
+# every array a fixture holds besides the scores (see tests/golden/make_golden.py)
+FIXTURE_OUTPUTS = ("moves", "sequence", "qstring", "bwd", "fwdbwd", "post", "states", "qual", "base_probs",
+                   "total_probs")

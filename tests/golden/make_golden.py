@@ -12,8 +12,13 @@ Outputs (all under tests/golden/):
                        fast-model options q_scale=0.97, q_shift=-1.8 of src/main.c:256-258).
                        The fp32 scores are exactly fp16 representable and stored as fp16.
   synth_<name>.npz     seeded synthetic fp16 scores with the reference CPU decoder's moves,
-                       sequence, qstring (openfish_decode_cpu) and its bwd / fwd+bwd / post
-                       tensors (src/decode_cpu.c:13-147).
+                       sequence, qstring (openfish_decode_cpu), its bwd / fwd+bwd / post
+                       tensors (src/decode_cpu.c:13-147) and the per-timestep outputs of its
+                       beam_search_cpu / generate_sequence_cpu (states, qual, base_probs,
+                       total_probs; src/beam_search.c:441-496, 49-99).  Cases whose options
+                       carry a temperature other than 1 were decoded with that value as
+                       beam_search_cpu's score_scale argument (src/beam_search.c:129,233), the
+                       one place the reference has for it (its own decoder passes 1.0f).
   rotary_small.npz     fp16 activations, sin/cos tables and openfish_rotary_emb_cpu's fp32 result.
 """
 import os
@@ -37,6 +42,8 @@ CASES = [
     ("fast_c320", 3, 64, 3, 104, 320, 1.0, {}),
     ("fast_stays", 3, 200, 2, 105, None, 0.3, dict(q_scale=0.97, q_shift=-1.8)),
     ("hac_cut10", 4, 64, 2, 106, None, 0.6, dict(beam_cut=10.0)),
+    ("fast_temp07", 3, 200, 3, 107, None, 0.8, dict(temperature=0.7)),
+    ("hac_temp16", 4, 96, 2, 108, None, 1.0, dict(temperature=1.6, q_scale=0.95, q_shift=-0.2)),
 ]
 
 
@@ -51,8 +58,12 @@ def main():
     for name, sl, T, N, seed, C, p_step, okw in CASES:
         sc = synth.make_scores(T, N, sl, seed, C=C, p_step=p_step)
         f = sc.astype(np.float32)
-        r = oracle.ref_decode(f, sl, oracle.decoder_init(**okw))
-        t = oracle.ref_scan_tensors(f, sl)
+        scale = float(okw.get("temperature", 1.0))
+        t = oracle.ref_decode_tensors(f, sl, oracle.decoder_init(**okw), score_scale=scale)
+        r = {k: t.pop(k) for k in ("moves", "sequence", "qstring")}
+        if scale == 1.0:  # the decoder's own entry point must say the same
+            whole = oracle.ref_decode(f, sl, oracle.decoder_init(**okw))
+            assert all(np.array_equal(whole[k], r[k]) for k in r)
         np.savez_compressed(os.path.join(OUT, "synth_%s.npz" % name), scores=sc,
                             state_len=sl, opt_keys=np.array(list(okw.keys()), dtype="U16"),
                             opt_values=np.array(list(okw.values()), dtype=np.float64),

@@ -41,10 +41,23 @@ def sequences(res):
     return [bytes(r[: int(m.sum())]) for r, m in zip(res["sequence"], res["moves"])]
 
 
+def _close(a, b, rtol, atol):
+    """|a - b| <= atol + rtol * |b|, with equal infinities (and paired NaNs) counting as equal."""
+    with np.errstate(invalid="ignore"):
+        ok = np.abs(a - b) <= atol + rtol * np.abs(b)
+    return ok | (a == b) | (np.isnan(a) & np.isnan(b))
+
+
 def compare(gpu, ref, post_atol=1e-3, post_rtol=1e-3, post_floor=1e-2):
     """Parity report.  Gates: bwd bit-exact; post within post_atol absolutely and within
     post_rtol relatively wherever the reference posterior is at least post_floor; moves and
-    sequence identical; qstring within +-1 on chunks whose sequence matches."""
+    sequence identical; qstring within +-1 on chunks whose sequence matches.  On chunks whose
+    moves and sequence match, also the per-timestep outputs (src/beam_search.c:441-496, 49-99):
+    states (the base at every timestep) identical; qual_data within 1e-3 absolutely;
+    total_probs within 1e-3 relatively; base_probs (-10 log10 of one minus a ratio of sums,
+    before scale and shift) within 1e-3 relatively or 0.02 of a Phred unit -- the logarithm
+    amplifies the last-ulp differences of the ratio once that ratio comes close to one, which is
+    why the absolute floor is there."""
     rep = {}
     if "bwd" in gpu and "bwd" in ref:
         rep["bwd_mismatch"] = int((gpu["bwd"] != ref["bwd"]).sum())
@@ -62,6 +75,15 @@ def compare(gpu, ref, post_atol=1e-3, post_rtol=1e-3, post_floor=1e-2):
     gs, rs = sequences(gpu), sequences(ref)
     rep["mismatches"] = [dict(chunk=int(i), edit_distance=edit_distance(gs[i], rs[i]))
                          for i in np.nonzero(~(same_moves & same_seq))[0]]
+    same = same_moves & same_seq
+    if "qual" in gpu and "qual" in ref and same.any():
+        rep["states_mismatch"] = int((gpu["states"][same] != ref["states"][same]).sum())
+        rep["qual_max_abs"] = float(np.abs(gpu["qual"][same] - ref["qual"][same]).max())
+        rep["total_probs_bad"] = int((~_close(gpu["total_probs"][same], ref["total_probs"][same], 1e-3, 0.0)).sum())
+        rep["base_probs_bad"] = int((~_close(gpu["base_probs"][same], ref["base_probs"][same], 1e-3, 2e-2)).sum())
+        with np.errstate(invalid="ignore"):
+            d = np.abs(gpu["base_probs"][same] - ref["base_probs"][same])
+        rep["base_probs_max_abs"] = float(np.nanmax(np.where(np.isfinite(d), d, 0.0)))
     if same_seq.any():
         dq = np.abs(gpu["qstring"][same_seq].astype(np.int32) - ref["qstring"][same_seq].astype(np.int32))
         rep["q_max_diff"] = int(dq.max())
@@ -80,3 +102,6 @@ def assert_parity(rep, min_identical=0.999, exact_bwd=True):
     need = int(np.ceil(min_identical * rep["chunks"]))
     assert rep["moves_equal"] >= need and rep["seq_equal"] >= need, rep
     assert rep["q_max_diff"] <= 1, rep
+    if "qual_max_abs" in rep:
+        assert rep["states_mismatch"] == 0 and rep["qual_max_abs"] <= 1e-3, rep
+        assert rep["total_probs_bad"] == 0 and rep["base_probs_bad"] == 0, rep

@@ -61,7 +61,15 @@ def test_struct_layouts_match_the_header(native_lib, tmp_path):
         }"""))
     exe = tmp_path / "layout"
     subprocess.run(["gcc", "-I", INC, str(src), "-o", str(exe)], check=True)
-    l1, l2, l3 = subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.splitlines()
+    text = subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout
+    l1, l2, l3 = text.splitlines()
+    # where a checkout of the reference is at hand, the same probe compiled against ITS header
+    # must print the same thing: layouts, DECODER_INIT and the log-level enum are the contract
+    ref_inc = os.path.join(os.environ.get("OPENFISH_REF", "/root/reference"), "include")
+    if os.path.exists(os.path.join(ref_inc, "openfish", "openfish.h")):
+        ref_exe = tmp_path / "layout_ref"
+        subprocess.run(["gcc", "-I", ref_inc, str(src), "-o", str(ref_exe)], check=True)
+        assert subprocess.run([str(ref_exe)], capture_output=True, text=True, check=True).stdout == text
     O = native_lib.Opt
     assert [int(x) for x in l1.split()] == [C.sizeof(O), O.beam_cut.offset, O.blank_score.offset,
                                             O.q_shift.offset, O.q_scale.offset, O.temperature.offset,

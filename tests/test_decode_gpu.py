@@ -15,10 +15,19 @@ from gpu_util import assert_parity, compare, gpu_decode, sequences
 
 pytestmark = pytest.mark.gpu
 
+# gpubuf fields holding the per-timestep outputs, under the oracle's names for them
+PER_TIMESTEP = (("qual", "qual_data"), ("states", "states"), ("base_probs", "base_probs"),
+                ("total_probs", "total_probs"))
+
 
 def check(of, oracle, sc16, sl, okw=None, threads=16, **gates):
     okw = okw or {}
-    ref = oracle.decode(sc16.astype(np.float32), sl, oracle.decoder_init(**okw), nthreads=threads, tensors=True)
+    # the library hands options->blank_score to its scans (as the reference's CUDA launcher does)
+    # and options->temperature to the beam search as its score_scale; the oracle has a switch for
+    # each, both of which are no-ops at the defaults 2.0 and 1.0
+    flags = oracle.SCAN_STAY_FROM_OPTIONS | oracle.TEMPERATURE_SCALES_SCORES
+    ref = oracle.decode(sc16.astype(np.float32), sl, oracle.decoder_init(**okw), nthreads=threads, tensors=True,
+                        flags=flags)
     out = gpu_decode(of, sc16, sl, of.decoder_init(**okw))
     rep = compare(out, ref)
     assert_parity(rep, **gates)
@@ -128,6 +137,17 @@ def test_long_chunks(native_lib, oracle_mod):
 def test_options(native_lib, oracle_mod, okw):
     from openfish_b200 import synth
     check(native_lib, oracle_mod, synth.make_scores(300, 6, 4, 81, p_step=0.7), 4, okw, min_identical=1.0)
+
+
+@pytest.mark.parametrize("okw", [dict(temperature=0.7), dict(temperature=1.6, beam_cut=20.0),
+                                 dict(blank_score=1.0), dict(blank_score=3.5, temperature=0.9)])
+def test_temperature_and_blank_score(native_lib, oracle_mod, okw):
+    # temperature is the reference beam search's score_scale argument (src/beam_search.c:129,233;
+    # pinned by the *_temp* fixtures, which the reference itself produced); blank_score also sets
+    # the scans' stay score, as in the reference's CUDA launcher (src/decode_cuda.cu:115)
+    from openfish_b200 import synth
+    check(native_lib, oracle_mod, synth.make_scores(350, 5, 3, 83, p_step=0.7), 3, okw, min_identical=1.0)
+    check(native_lib, oracle_mod, synth.make_scores(200, 3, 4, 84, p_step=0.9), 4, okw, min_identical=1.0)
 
 
 def test_into_and_submit_wait_match_decode_gpu(native_lib):
@@ -254,7 +274,8 @@ def test_full_size_hac_properties_and_parity(native_lib, oracle_mod):
         assert set(bytes(s[: lens[n]])) <= set(b"ACGT") and not s[lens[n]:].any() and not q[lens[n]:].any()
         assert q[: lens[n]].min() >= 34 and q[: lens[n]].max() <= 83
     # the oracle on the whole batch, tensors included (backward scores must be bit-identical)
-    full = dict(a, bwd=gb.tensor("bwd_NTC").cpu().numpy(), post=gb.tensor("post_NTC").cpu().numpy())
+    full = dict(a, bwd=gb.tensor("bwd_NTC").cpu().numpy(), post=gb.tensor("post_NTC").cpu().numpy(),
+                **{k: gb.tensor(name).cpu().numpy() for k, name in PER_TIMESTEP})
     gb.free()
     ref = oracle_mod.decode(d.float().cpu().numpy(), sl, nthreads=os.cpu_count() or 8, tensors=True)
     rep = compare(full, ref)
@@ -267,6 +288,33 @@ def test_full_size_hac_properties_and_parity(native_lib, oracle_mod):
     alone = gpu_decode(of, sub16, sl, tensors=False)
     for k in a:
         assert np.array_equal(alone[k], a[k][idx])
+
+
+@pytest.mark.parametrize("sl,N,seed,piece", [(5, 256, 0x0F17, 64), (3, 1024, 0x0F15, 512)])
+def test_full_size_sup_and_fast_parity(native_lib, oracle_mod, sl, N, seed, piece):
+    """The other two BASELINE-sized batches at T = 1666 (sup N = 256, fast N = 1024): one decode of
+    the whole batch on the GPU, every chunk against the oracle (which takes the batch in pieces to
+    bound host memory), same gates as the hac batch."""
+    import torch
+    from openfish_b200 import synth
+    of = native_lib
+    T = 1666
+    d = synth.make_scores_device(T, N, sl, seed, "cuda")
+    gb = of.gpubuf_init(T, N, sl)
+    a = of.decode_gpu(d, sl, gpubuf=gb)
+    names = (("bwd", "bwd_NTC"), ("post", "post_NTC")) + PER_TIMESTEP
+    identical = 0
+    for lo in range(0, N, piece):
+        hi = min(N, lo + piece)
+        got = {k: v[lo:hi] for k, v in a.items()}
+        got.update({k: gb.tensor(name)[lo:hi].cpu().numpy() for k, name in names})
+        ref = oracle_mod.decode(d[:, lo:hi, :].float().cpu().numpy(), sl, nthreads=os.cpu_count() or 8, tensors=True)
+        rep = compare(got, ref)
+        assert_parity(rep, min_identical=0.999)
+        identical += min(rep["moves_equal"], rep["seq_equal"])
+        del got, ref
+    gb.free()
+    assert identical == N  # every chunk has been identical so far; the gate itself is 99.9 %
 
 
 def test_hardware_approximations_are_within_the_certificates_bounds(native_lib):

@@ -58,6 +58,21 @@ def test_odd_shapes_take_the_scalar_path(native_lib, oracle_mod, B, S, H, D, hal
     assert close(out, ref)
 
 
+def test_full_size_against_the_oracle(native_lib, oracle_mod):
+    # the encoder's whole packed QKV tensor [32][1666][3][8][64] (BASELINE configuration 4) against
+    # the CPU routine on the same fp16 values, every element
+    import torch
+    B, S, H, D = 32, 1666, 8, 64
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = torch.randn((B, S, 3, H, D), generator=g, device="cuda", dtype=torch.float32).half()
+    ref = x.float().cpu().numpy()
+    sin, cos = tables(S, D // 2)
+    oracle_mod.rotary(ref.reshape(-1), sin, cos, D // 2, S * 3 * H * D, 3 * H * D, D, B, S, 2 * H)
+    native_lib.rotary_emb_gpu(x, torch.from_numpy(sin).cuda(), torch.from_numpy(cos).cuda(), B, S, 2 * H, D,
+                              D // 2, S * 3 * H * D, 3 * H * D, D)
+    assert close(x.cpu().numpy(), ref)
+
+
 def test_full_size_round_trip(native_lib):
     # config-sized tensor: rotating by +theta then by -theta gives the input back up to two
     # fp16 roundings
