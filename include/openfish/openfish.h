@@ -66,9 +66,22 @@ typedef struct openfish_gpubuf {
 
 /* Decoder options (reference include/openfish/openfish.h:29-37).  Like the reference, the
  * decoder reads beam_cut, blank_score, q_shift and q_scale (reference
- * src/decode_cuda.cu:133-136); the beam width is fixed at 32 (reference src/decode.h:49), and
- * temperature and move_pad are not used.  A beam_width other than 32 is reported as an error
- * instead of being silently ignored. */
+ * src/decode_cuda.cu:133-136); the beam width is fixed at 32 (reference src/decode.h:49) and a
+ * beam_width other than 32 is reported as an error instead of being silently ignored; move_pad
+ * is not used.
+ *
+ * Two fields reach further here than in the reference's CPU decoder, the decoder whose results
+ * this library otherwise reproduces.  At their DECODER_INIT values nothing differs.
+ *   blank_score  is also the stay score of the two scans, as in the reference's CUDA launcher
+ *                (reference src/decode_cuda.cu:115); the reference's CPU scans use the literal
+ *                2.0 whatever the option says (reference src/decode_cpu.c:14,56).  Results equal
+ *                the CPU decoder's at blank_score = 2.0 only.
+ *   temperature  multiplies every transition score inside the beam search: it is handed to the
+ *                search as the score_scale argument the reference's beam_search_cpu has
+ *                (reference src/beam_search.c:129,233) and that the reference's decoders always
+ *                pass as 1.0 (reference src/decode_cpu.c:216, src/decode_cuda.cu:165), ignoring
+ *                the option.  The scans are not scaled.  Results equal the reference's at
+ *                temperature = 1.0 only. */
 typedef struct openfish_opt {
     size_t beam_width;
     float beam_cut;

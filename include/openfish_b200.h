@@ -60,6 +60,25 @@ void openfish_b200_decode_submit(int T, int N, int C, const void *scores_TNC, in
                                  uint8_t *moves, char *sequence, char *qstring);
 void openfish_b200_decode_wait(const openfish_gpubuf_t *gpubuf);
 
+/* Submit for callers that produce the scores on a CUDA stream of their own.  The calls above run
+ * on a stream that is ordered after the legacy default stream only (where the reference does all
+ * its work): scores written by a kernel on any other stream -- a non-blocking one in particular,
+ * as every side stream of a deep-learning framework is -- are not waited for unless the caller
+ * synchronises first.  This variant takes that stream (a cudaStream_t, passed as void * so that
+ * this header needs no CUDA header) and makes the decode wait, on the device, for everything
+ * queued on it so far; the host does not wait.  No counterpart in the reference, which
+ * synchronises the whole device around every kernel (reference src/decode_cuda.cu:152-211). */
+void openfish_b200_decode_submit_on(void *cuda_stream, int T, int N, int C, const void *scores_TNC,
+                                    int state_len, const openfish_opt_t *options,
+                                    const openfish_gpubuf_t *gpubuf, uint8_t *moves, char *sequence,
+                                    char *qstring);
+
+/* The other direction: makes cuda_stream wait, on the device, for the gpubuf's decode in flight
+ * (a no-op when there is none).  Work queued on that stream afterwards -- overwriting the scores
+ * with the next batch, reading the gpubuf's tensors -- then runs after the decode.  The results
+ * in the host buffers still need openfish_b200_decode_wait. */
+void openfish_b200_stream_wait_decode(void *cuda_stream, const openfish_gpubuf_t *gpubuf);
+
 /* Device time, in milliseconds, of the gpubuf's last completed decode, measured with CUDA
  * events on the streams the kernels ran on: ms[0] backward scan kernel, ms[1] everything between
  * it and the copies (the beam search kernel with the forward scan kernel beside it on a second
@@ -86,6 +105,18 @@ float openfish_b200_last_rotary_ms(void);
 #define OPENFISH_B200_EX2_REL_BOUND 2.384185791015625e-07 /* 2^-22 */
 #define OPENFISH_B200_LG2_ABS_BOUND 2.828e-07             /* 2^-21.75 */
 int openfish_b200_selfcheck_arith(double err[2]);
+
+/* Self-check of the path by which a kernel reports that a wait ran out.  Every wait of a kernel
+ * for an asynchronous copy is bounded (two seconds); when one runs out the kernel raises a status
+ * word, ends normally, and the decode's completion reports OPENFISH_B200_ERR_DEVICE_WAIT.  This
+ * call runs, on the gpubuf's stream and status word, a one-block kernel whose only act is such a
+ * wait, limit_us microseconds long, on a barrier that nothing will ever complete (no copy is
+ * issued), and then reads the status exactly as openfish_b200_decode_wait does.  It returns
+ * OPENFISH_B200_ERR_DEVICE_WAIT when the machinery works (and has cleared the status word again,
+ * so the gpubuf decodes normally afterwards), OPENFISH_B200_OK if the wait did not run out.
+ * Nothing faults, traps or hangs.  Does not touch openfish_b200_last_status().  No counterpart in
+ * the reference, whose kernels do not wait. */
+int openfish_b200_selfcheck_wait(const openfish_gpubuf_t *gpubuf, unsigned limit_us);
 
 /* Number of kernels one decode call launches (for benchmark bookkeeping). */
 int openfish_b200_kernels_per_decode(void);

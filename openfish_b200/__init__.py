@@ -74,6 +74,12 @@ def lib():
         for name in ("openfish_b200_decode_into", "openfish_b200_decode_submit"):
             getattr(L, name).restype = None
             getattr(L, name).argtypes = dec + [vp] * 3
+        L.openfish_b200_decode_submit_on.restype = None
+        L.openfish_b200_decode_submit_on.argtypes = [vp] + dec + [vp] * 3
+        L.openfish_b200_stream_wait_decode.restype = None
+        L.openfish_b200_stream_wait_decode.argtypes = [vp, C.POINTER(GpuBufStruct)]
+        L.openfish_b200_selfcheck_wait.restype = i
+        L.openfish_b200_selfcheck_wait.argtypes = [C.POINTER(GpuBufStruct), C.c_uint]
         L.openfish_b200_decode_wait.restype = None
         L.openfish_b200_decode_wait.argtypes = [C.POINTER(GpuBufStruct)]
         L.openfish_rotary_emb_gpu.restype = None
@@ -188,13 +194,32 @@ def decode_gpu(scores_TNC, state_len, options=None, gpubuf=None):
             gpubuf.free()
 
 
-def decode_into(scores_TNC, state_len, gpubuf, moves, sequence, qstring, options=None, wait=True):
-    """openfish_b200_decode_into / _submit: results into caller-owned uint8 host tensors
-    [N][T] (torch, ideally pinned).  With wait=False call decode_wait(gpubuf) afterwards."""
+def decode_into(scores_TNC, state_len, gpubuf, moves, sequence, qstring, options=None, wait=True, stream=None):
+    """openfish_b200_decode_into / _submit / _submit_on: results into caller-owned uint8 host
+    tensors [N][T] (torch, ideally pinned).  With wait=False call decode_wait(gpubuf) afterwards.
+    stream (a torch.cuda.Stream, implies wait=False): the stream the scores were produced on; the
+    decode is ordered after the work queued on it."""
     args = _scores_args(scores_TNC, state_len, options, gpubuf)
-    fn = lib().openfish_b200_decode_into if wait else lib().openfish_b200_decode_submit
-    fn(*args, moves.data_ptr(), sequence.data_ptr(), qstring.data_ptr())
+    out = (moves.data_ptr(), sequence.data_ptr(), qstring.data_ptr())
+    if stream is not None:
+        lib().openfish_b200_decode_submit_on(stream.cuda_stream, *args, *out)
+    else:
+        fn = lib().openfish_b200_decode_into if wait else lib().openfish_b200_decode_submit
+        fn(*args, *out)
     _check()
+
+
+def stream_wait_decode(stream, gpubuf):
+    """openfish_b200_stream_wait_decode: work queued on `stream` from now on runs after the
+    gpubuf's decode in flight."""
+    lib().openfish_b200_stream_wait_decode(stream.cuda_stream, gpubuf.ptr)
+    _check()
+
+
+def selfcheck_wait(gpubuf, limit_us=1000):
+    """openfish_b200_selfcheck_wait: the status code (ERR_DEVICE_WAIT = 7 when the path from a
+    kernel's wait that ran out to the host's error works)."""
+    return int(lib().openfish_b200_selfcheck_wait(gpubuf.ptr, limit_us))
 
 
 def decode_static(scores_TNC, state_len, moves_gpu, sequence_gpu, qstring_gpu, options=None):

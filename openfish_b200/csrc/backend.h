@@ -15,6 +15,8 @@ extern "C" {
 
 int ofb_gpubuf_create(int T, int N, int state_len, openfish_gpubuf_t **out);
 int ofb_gpubuf_destroy(openfish_gpubuf_t *gpubuf);
+/* Checks that gpubuf came from ofb_gpubuf_create (whatever its shape). */
+int ofb_gpubuf_check_owner(const openfish_gpubuf_t *gpubuf);
 /* Checks that gpubuf came from ofb_gpubuf_create with this shape. */
 int ofb_gpubuf_check(const openfish_gpubuf_t *gpubuf, int T, int N, int state_len);
 
@@ -33,6 +35,12 @@ int ofb_decode_submit(int T, int N, int C, const void *scores, int state_len,
 /* Wait for the gpubuf's decode in flight; returns its status (device-side status included). */
 int ofb_decode_wait(const openfish_gpubuf_t *gpubuf);
 int ofb_last_decode_ms(const openfish_gpubuf_t *gpubuf, float ms[8]);
+/* Makes `stream` (a cudaStream_t) wait, on the device, for the gpubuf's decode in flight. */
+int ofb_stream_wait_decode(void *stream, const openfish_gpubuf_t *gpubuf);
+/* Runs, on the gpubuf's stream and status word, a one-block kernel whose only act is a bounded wait
+ * (limit_us microseconds) on a barrier nothing will ever complete, then reads the status the way a
+ * decode's completion does.  Returns OPENFISH_B200_ERR_DEVICE_WAIT when the machinery works. */
+int ofb_selfcheck_wait(const openfish_gpubuf_t *gpubuf, unsigned limit_us);
 
 int ofb_rotary(void *x, const void *sin_t, const void *cos_t, int batch, int seqlen, int nheads,
                int rotary_half, long long stride_batch, long long stride_seq,

@@ -23,6 +23,7 @@ struct OfDecodeArgs {
     float *total_probs;        // [N][T] out
     const ofx::Tables *tables;
     int *status;
+    uint64_t wait_ns;          // how long a kernel waits for an asynchronous copy before raising *status
     int T, N, C, state_len;
     float stay, log_beam_cut, q_shift, q_scale;
     float score_scale;         // multiplies every transition score in the beam search (src/beam_search.c:233)

@@ -145,11 +145,12 @@ beam_search_kernel(const OfDecodeArgs a) {
             // the beam search strides timesteps by N*C (src/decode_cpu.c:204,216)
             const __half *beam_scores = a.scores + (size_t)chunk * NS * 4;
             const size_t beam_stride = (size_t)N * a.C;
-            for (int t = 0; t <= T; ++t) {
+            int issued = 0;
+            for (int t = 0; t <= T; ++t, ++issued) {
                 const int slot = t % RING;
                 if (t >= RING)
                     ofd::mbar_wait_bounded(&sm.empty[slot], (uint32_t)(t / RING - 1) & 1u,
-                                           &sm.abort_flag, a.status);
+                                           &sm.abort_flag, a.status, a.wait_ns);
                 if (sm.abort_flag) break;
                 const uint32_t bytes = Smem::kBwdRow + (t < T ? Smem::kScoreRow : 0);
                 ofd::mbar_arrive_expect_tx(&sm.full[slot], bytes);
@@ -158,13 +159,15 @@ beam_search_kernel(const OfDecodeArgs a) {
                     ofd::bulk_g2s(sm.score_ring[slot], beam_scores + beam_stride * t, Smem::kScoreRow,
                                   &sm.full[slot]);
             }
+            // after an abort: the newest copies get a bounded chance to land before the block retires
+            if (sm.abort_flag) ofd::mbar_drain_bounded(sm.full, RING, issued, a.wait_ns);
         }
         return;
     }
     // ------------------------------------------------------------------ beam warp
     const ofx::TabRef tr = {sm.exp2_j, 1, sm.rcp_c, sm.log_c};
     const uint32_t lt_mask = (1u << lane) - 1u;
-    ofd::mbar_wait_bounded(&sm.full[0], 0, &sm.abort_flag, a.status);
+    ofd::mbar_wait_bounded(&sm.full[0], 0, &sm.abort_flag, a.status, a.wait_ns);
     // initial beam: first <= 32 states, in state order, reaching the 32nd largest bwd[0]
     // (src/beam_search.c:151-175).  Radix-select the 32nd largest key bit by bit.
     {
@@ -203,7 +206,7 @@ beam_search_kernel(const OfDecodeArgs a) {
     for (int t = 0; t < T; ++t) {
         const int slot_a = t % RING, slot_b = (t + 1) % RING;
         // row t was confirmed when it served as "next row" one step ago (or before the loop)
-        ofd::mbar_wait_bounded(&sm.full[slot_b], (uint32_t)((t + 1) / RING) & 1u, &sm.abort_flag, a.status);
+        ofd::mbar_wait_bounded(&sm.full[slot_b], (uint32_t)((t + 1) / RING) & 1u, &sm.abort_flag, a.status, a.wait_ns);
         const __half *srow = reinterpret_cast<const __half *>(sm.score_ring[slot_a]);
         const float *brow = reinterpret_cast<const float *>(sm.bwd_ring[slot_b]);
         const bool act = lane < W;

@@ -34,8 +34,9 @@ struct GpuBuf {
     int T, N, state_len, device;
     cudaStream_t stream;   // everything but the forward scan; blocking, see ofb_gpubuf_create
     cudaStream_t stream2;  // the forward scan, ordered against `stream` by events only
-    cudaEvent_t ev[7];     // 0 start, 1 bwd scan done, 2 beam search done, 3 sequence done, 4 copies done,
-                           // 5 fwd scan start, 6 fwd scan done
+    cudaEvent_t ev[8];     // 0 start, 1 bwd scan done, 2 beam search done, 3 sequence done, 4 copies done,
+                           // 5 fwd scan start, 6 fwd scan done, 7 the caller's stream at submit time
+    uint64_t wait_ns;      // how long a kernel waits for an asynchronous copy before it raises d_status
     int *d_init_kmers;     // inside the beam_vector allocation, behind the back-pointers
     ofx::Tables *d_tables;
     float *d_fwd;              // forward scores [N][T+1][ns]: scan kernel -> posterior kernel (64-state model
@@ -100,7 +101,7 @@ int destroy(GpuBuf *g) {
     cudaFree(g->d_fwd);
     cudaFree(g->d_status);
     if (g->h_stage) cudaFreeHost(g->h_stage);
-    for (int i = 0; i < 7; ++i)
+    for (int i = 0; i < 8; ++i)
         if (g->ev[i]) cudaEventDestroy(g->ev[i]);
     if (g->stream2) cudaStreamDestroy(g->stream2);
     if (g->stream) cudaStreamDestroy(g->stream);
@@ -129,7 +130,8 @@ extern "C" int ofb_gpubuf_create(int T, int N, int state_len, openfish_gpubuf_t 
         // stream (where the reference runs), so freshly written scores are seen
         CU(cudaStreamCreateWithFlags(&g->stream, cudaStreamDefault));
         CU(cudaStreamCreateWithFlags(&g->stream2, cudaStreamNonBlocking));
-        for (int i = 0; i < 7; ++i) CU(cudaEventCreate(&g->ev[i]));
+        for (int i = 0; i < 8; ++i) CU(cudaEventCreate(&g->ev[i]));
+        g->wait_ns = ofd::kDefaultWaitLimitNs;
         // same ten buffers and sizes as the reference (src/decode_cuda.cu:22-45); the three
         // result arrays share one allocation so that one copy brings them back
         CU(cudaMalloc(&g->pub.bwd_NTC, tens));
@@ -178,6 +180,12 @@ extern "C" int ofb_gpubuf_destroy(openfish_gpubuf_t *gpubuf) {
     return destroy(g);
 }
 
+extern "C" int ofb_gpubuf_check_owner(const openfish_gpubuf_t *gpubuf) {
+    if (!gpubuf) return fail(OPENFISH_B200_ERR_ARGUMENT, "gpubuf is NULL");
+    if (priv(gpubuf)->magic != kMagic) return fail(OPENFISH_B200_ERR_ARGUMENT, "gpubuf was not created by openfish_gpubuf_init");
+    return OPENFISH_B200_OK;
+}
+
 extern "C" int ofb_gpubuf_check(const openfish_gpubuf_t *gpubuf, int T, int N, int state_len) {
     if (!gpubuf) return fail(OPENFISH_B200_ERR_ARGUMENT, "gpubuf is NULL");
     const GpuBuf *g = priv(gpubuf);
@@ -216,6 +224,7 @@ extern "C" int ofb_decode_submit(int T, int N, int C, const void *scores, int st
     a.total_probs = g->pub.total_probs;
     a.tables = g->d_tables;
     a.status = g->d_status;
+    a.wait_ns = g->wait_ns;
     a.T = T; a.N = N; a.C = C; a.state_len = state_len;
     a.stay = blank_score;
     a.log_beam_cut = beam_cut > 0.0f ? logf(beam_cut) : 3.402823466e+38f;  // src/beam_search.c:135
@@ -226,18 +235,27 @@ extern "C" int ofb_decode_submit(int T, int N, int C, const void *scores, int st
     // stream:  backward scan -> beam search ----------------------> posterior + sequence -> copies
     // stream2:                  forward scan (beside the beam search) --^
     // (for hac and sup the forward scan kernel also writes the posterior, and a.fwd is null)
+    // Ordering against the producer of the scores: the gpubuf's main stream is a blocking one, so it
+    // runs after whatever the caller queued on the legacy default stream (the reference's stream);
+    // a caller that works on a stream of its own names it, and the decode waits for that stream's
+    // work as of now.
+    if (params->on_caller_stream) {
+        cudaStream_t caller = static_cast<cudaStream_t>(params->caller_stream);
+        CU(cudaEventRecord(g->ev[7], caller));
+        CU(cudaStreamWaitEvent(g->stream, g->ev[7], 0));
+    }
     CU(cudaEventRecord(g->ev[0], g->stream));
     CU(of_launch_scans(scores, g->pub.bwd_NTC, nullptr, T, N, state_len, blank_score, g->d_tables,
-                       g->d_status, g->stream));
+                       g->d_status, g->wait_ns, g->stream));
     CU(cudaEventRecord(g->ev[1], g->stream));
     CU(cudaStreamWaitEvent(g->stream2, g->ev[1], 0));
     CU(cudaEventRecord(g->ev[5], g->stream2));
     if (of_forward_posterior_fused(state_len))
         CU(of_launch_forward_posterior(scores, g->pub.bwd_NTC, g->pub.post_NTC, T, N, state_len, blank_score,
-                                       g->d_tables, g->d_status, g->stream2));
+                                       g->d_tables, g->d_status, g->wait_ns, g->stream2));
     else
         CU(of_launch_scans(scores, nullptr, g->d_fwd, T, N, state_len, blank_score, g->d_tables,
-                           g->d_status, g->stream2));
+                           g->d_status, g->wait_ns, g->stream2));
     CU(cudaEventRecord(g->ev[6], g->stream2));
     CU(of_launch_beam_search(a, g->stream));
     CU(cudaEventRecord(g->ev[2], g->stream));
@@ -263,17 +281,28 @@ extern "C" int ofb_decode_submit(int T, int N, int C, const void *scores, int st
     return OPENFISH_B200_OK;
 }
 
+namespace {
+// Waits for the gpubuf's main stream, then looks at the status word its kernels share (copied to
+// the host by the last operation queued): a raised status is reported and cleared on the device.
+int stream_done_and_status(GpuBuf *g) {
+    CU(cudaStreamSynchronize(g->stream));
+    if (*g->h_status != ofd::kStatusOk) {
+        const int st = *g->h_status;
+        *g->h_status = ofd::kStatusOk;
+        CU(cudaMemsetAsync(g->d_status, 0, sizeof(int), g->stream));
+        return fail(OPENFISH_B200_ERR_DEVICE_WAIT, "a kernel raised device status %d (an asynchronous copy did not complete in time)", st);
+    }
+    return OPENFISH_B200_OK;
+}
+}  // namespace
+
 extern "C" int ofb_decode_wait(const openfish_gpubuf_t *gpubuf) {
     GpuBuf *g = priv(gpubuf);
     if (!g->pending) return OPENFISH_B200_OK;
     g->pending = false;
-    CU(cudaStreamSynchronize(g->stream));
+    const int rc = stream_done_and_status(g);
+    if (rc != OPENFISH_B200_OK) return rc;
     const size_t nt = (size_t)g->N * g->T;
-    if (*g->h_status != ofd::kStatusOk) {
-        const int st = *g->h_status;
-        cudaMemsetAsync(g->d_status, 0, sizeof(int), g->stream);
-        return fail(OPENFISH_B200_ERR_DEVICE_WAIT, "decode kernel raised device status %d (an asynchronous copy did not complete in time)", st);
-    }
     if (g->via_stage) {
         memcpy(g->dst_moves, g->h_stage, nt);
         memcpy(g->dst_sequence, g->h_stage + nt, nt);
@@ -294,6 +323,24 @@ extern "C" int ofb_decode_wait(const openfish_gpubuf_t *gpubuf) {
     g->ms[6] = from_beam < from_fwd ? from_beam : from_fwd;
     g->ms[7] = 0.f;
     return OPENFISH_B200_OK;
+}
+
+extern "C" int ofb_stream_wait_decode(void *stream, const openfish_gpubuf_t *gpubuf) {
+    GpuBuf *g = priv(gpubuf);
+    if (!g->pending) return OPENFISH_B200_OK;  // nothing in flight: nothing to wait for
+    CU(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), g->ev[4], 0));
+    return OPENFISH_B200_OK;
+}
+
+extern "C" int ofb_selfcheck_wait(const openfish_gpubuf_t *gpubuf, unsigned limit_us) {
+    GpuBuf *g = priv(gpubuf);
+    if (g->pending) return fail(OPENFISH_B200_ERR_ARGUMENT, "a decode is in flight on this gpubuf");
+    int dev = -1;
+    CU(cudaGetDevice(&dev));
+    if (dev != g->device) return fail(OPENFISH_B200_ERR_ARGUMENT, "gpubuf belongs to device %d, current device is %d", g->device, dev);
+    CU(of_launch_wait_that_runs_out(g->d_status, (uint64_t)limit_us * 1000ull, g->stream));
+    CU(cudaMemcpyAsync(g->h_status, g->d_status, sizeof(int), cudaMemcpyDeviceToHost, g->stream));
+    return stream_done_and_status(g);
 }
 
 extern "C" int ofb_last_decode_ms(const openfish_gpubuf_t *gpubuf, float ms[8]) {

@@ -133,7 +133,7 @@ extern "C" int openfish_b200_decode_static(int T, int N, int C, const void *scor
     e = cudaMemsetAsync(status, 0, sizeof(int), stream);  // the one thing that must start at zero
     if (e == cudaSuccess)
         e = of_launch_scans(scores_TNC, bwd, fwd, T, N, state_len, options->blank_score, tables,
-                            status, stream);
+                            status, ofd::kDefaultWaitLimitNs, stream);
     if (e == cudaSuccess) {
         OfDecodeArgs a;
         a.scores = static_cast<const __half *>(scores_TNC);
@@ -151,6 +151,7 @@ extern "C" int openfish_b200_decode_static(int T, int N, int C, const void *scor
         a.total_probs = reinterpret_cast<float *>(base + o_total);
         a.tables = tables;
         a.status = status;
+        a.wait_ns = ofd::kDefaultWaitLimitNs;
         a.T = T; a.N = N; a.C = C; a.state_len = state_len;
         a.stay = options->blank_score;
         a.log_beam_cut = options->beam_cut > 0.0f ? logf(options->beam_cut) : 3.402823466e+38f;

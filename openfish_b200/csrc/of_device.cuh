@@ -50,12 +50,17 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     return t;
 }
 
-// Wait for phase `parity` of `bar`, but never for longer than about two seconds and never once
+// How long a kernel waits for one asynchronous copy before it gives up, unless the host says
+// otherwise: far beyond anything a healthy device needs (a copy takes microseconds).
+constexpr uint64_t kDefaultWaitLimitNs = 2000000000ull;
+
+// Wait for phase `parity` of `bar`, but never for longer than `limit_ns` and never once
 // the block's abort flag is up.  On timeout the abort flag and the global status word are set
 // and the caller carries on (with meaningless data) so that every barrier in the kernel is
 // still reached and the kernel ends; the host then reports the status instead of results.
 __device__ __forceinline__ void mbar_wait_bounded(uint64_t *bar, uint32_t parity,
-                                                  volatile int *abort_flag, int *status) {
+                                                  volatile int *abort_flag, int *status,
+                                                  uint64_t limit_ns) {
     if (mbar_try_wait(bar, parity)) return;
     uint64_t t0 = 0;
     for (uint32_t spin = 1;; ++spin) {
@@ -65,11 +70,25 @@ __device__ __forceinline__ void mbar_wait_bounded(uint64_t *bar, uint32_t parity
             __nanosleep(64);
             const uint64_t now = global_timer_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > 2000000000ull) {
+            else if (now - t0 > limit_ns) {
                 *abort_flag = 1;
                 atomicExch(status, kStatusWaitTimeout);
                 return;
             }
+        }
+    }
+}
+
+// After an abort: give the copies this thread issued last (the newest into each ring slot; copy
+// number i went to barrier i % ring with phase parity (i / ring) & 1) one more bounded chance to
+// land, so that none of them is still writing into the block's shared memory when the block
+// retires and the memory passes to another block.  `issued` = copies issued so far, in order.
+__device__ __forceinline__ void mbar_drain_bounded(uint64_t *bars, int ring, int issued, uint64_t limit_ns) {
+    const uint64_t t0 = global_timer_ns();
+    for (int i = issued > ring ? issued - ring : 0; i < issued; ++i) {
+        while (!mbar_try_wait(&bars[i % ring], (uint32_t)(i / ring) & 1u)) {
+            __nanosleep(64);
+            if (global_timer_ns() - t0 > limit_ns) return;
         }
     }
 }
@@ -84,8 +103,27 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
         : "memory");
 }
 
-__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+// Named barriers (ids 1..15; 0 is __syncthreads): N threads (a multiple of 32) take part in each
+// round, some of which may only announce themselves (arrive) and carry on.  Ids and counts are
+// compile-time constants so that a kernel reserves only the barriers it names.
+template <int ID, int N>
+__device__ __forceinline__ void named_bar_sync() {
+    asm volatile("bar.sync %0, %1;" ::"n"(ID), "n"(N) : "memory");
+}
+template <int ID, int N>
+__device__ __forceinline__ void named_bar_arrive() {
+    asm volatile("bar.arrive %0, %1;" ::"n"(ID), "n"(N) : "memory");
+}
+// the same for a pair of barriers ID, ID + 1 picked at run time
+template <int ID, int N>
+__device__ __forceinline__ void named_bar_sync2(int which) {
+    if (which) named_bar_sync<ID + 1, N>();
+    else named_bar_sync<ID, N>();
+}
+template <int ID, int N>
+__device__ __forceinline__ void named_bar_arrive2(int which) {
+    if (which) named_bar_arrive<ID + 1, N>();
+    else named_bar_arrive<ID, N>();
 }
 
 // Order-preserving map float -> int32 (and back) so integer warp reductions can take a max.

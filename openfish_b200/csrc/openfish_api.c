@@ -114,20 +114,48 @@ void openfish_gpubuf_free(openfish_gpubuf_t *gpubuf) {
     backend_failed(__func__, ofb_gpubuf_destroy(gpubuf));
 }
 
+static void submit(const char *func, int on_stream, void *cuda_stream, int T, int N, int C,
+                   const void *scores_TNC, int state_len, const openfish_opt_t *options,
+                   const openfish_gpubuf_t *gpubuf, uint8_t *moves, char *sequence, char *qstring) {
+    clear_error();
+    if (!moves || !sequence || !qstring) {
+        raise_error(func, OPENFISH_B200_ERR_ARGUMENT, "result buffers must not be NULL");
+        return;
+    }
+    if (check_decode_args(func, T, N, C, scores_TNC, state_len, options, gpubuf)) return;
+    trace(func, "scores tensor dim: %d, %d, %d", T, N, C);
+    const ofb_decode_params_t params = {options->beam_cut, options->blank_score, options->q_shift,
+                                        options->q_scale, options->temperature, on_stream, cuda_stream};
+    backend_failed(func, ofb_decode_submit(T, N, C, scores_TNC, state_len, &params, gpubuf, moves,
+                                           sequence, qstring));
+}
+
 void openfish_b200_decode_submit(int T, int N, int C, const void *scores_TNC, int state_len,
                                  const openfish_opt_t *options, const openfish_gpubuf_t *gpubuf,
                                  uint8_t *moves, char *sequence, char *qstring) {
+    submit(__func__, 0, NULL, T, N, C, scores_TNC, state_len, options, gpubuf, moves, sequence, qstring);
+}
+
+void openfish_b200_decode_submit_on(void *cuda_stream, int T, int N, int C, const void *scores_TNC,
+                                    int state_len, const openfish_opt_t *options,
+                                    const openfish_gpubuf_t *gpubuf, uint8_t *moves, char *sequence,
+                                    char *qstring) {
+    submit(__func__, 1, cuda_stream, T, N, C, scores_TNC, state_len, options, gpubuf, moves, sequence, qstring);
+}
+
+void openfish_b200_stream_wait_decode(void *cuda_stream, const openfish_gpubuf_t *gpubuf) {
     clear_error();
-    if (!moves || !sequence || !qstring) {
-        raise_error(__func__, OPENFISH_B200_ERR_ARGUMENT, "result buffers must not be NULL");
+    if (!gpubuf) {
+        raise_error(__func__, OPENFISH_B200_ERR_ARGUMENT, "gpubuf is NULL");
         return;
     }
-    if (check_decode_args(__func__, T, N, C, scores_TNC, state_len, options, gpubuf)) return;
-    trace(__func__, "scores tensor dim: %d, %d, %d", T, N, C);
-    const ofb_decode_params_t params = {options->beam_cut, options->blank_score, options->q_shift,
-                                        options->q_scale, options->temperature, 0, NULL};
-    backend_failed(__func__, ofb_decode_submit(T, N, C, scores_TNC, state_len, &params, gpubuf, moves,
-                                               sequence, qstring));
+    if (backend_failed(__func__, ofb_gpubuf_check_owner(gpubuf))) return;
+    backend_failed(__func__, ofb_stream_wait_decode(cuda_stream, gpubuf));
+}
+
+int openfish_b200_selfcheck_wait(const openfish_gpubuf_t *gpubuf, unsigned limit_us) {
+    if (!gpubuf || ofb_gpubuf_check_owner(gpubuf) != OPENFISH_B200_OK) return OPENFISH_B200_ERR_ARGUMENT;
+    return ofb_selfcheck_wait(gpubuf, limit_us);
 }
 
 void openfish_b200_decode_wait(const openfish_gpubuf_t *gpubuf) {

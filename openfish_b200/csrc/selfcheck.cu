@@ -7,7 +7,9 @@
 
 #include "backend.h"
 #include "fast_lse.cuh"
+#include "of_device.cuh"
 #include "openfish_b200.h"
+#include "scan.cuh"
 
 namespace {
 
@@ -44,7 +46,24 @@ __global__ void lg2_error_kernel(double *out, unsigned first, unsigned last) {
     atomic_max_double(out, worst);
 }
 
+// A bounded wait on a barrier for which nothing was ever issued: it has to run out.
+__global__ void wait_that_runs_out_kernel(int *status, uint64_t wait_ns) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        ofd::mbar_init(&bar, 1);
+        ofd::mbar_fence_init();
+        ofd::mbar_wait_bounded(&bar, 0u, &abort_flag, status, wait_ns);
+    }
+}
+
 }  // namespace
+
+cudaError_t of_launch_wait_that_runs_out(int *status, uint64_t wait_ns, cudaStream_t stream) {
+    wait_that_runs_out_kernel<<<1, 32, 0, stream>>>(status, wait_ns);
+    return cudaGetLastError();
+}
 
 extern "C" int ofb_selfcheck_arith(double err[2]) {
     double *d = nullptr;

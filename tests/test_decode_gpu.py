@@ -218,6 +218,56 @@ def test_decodes_from_several_host_threads_and_in_flight(native_lib):
         g.free()
 
 
+def test_submit_on_a_caller_stream_without_a_host_sync(native_lib):
+    # scores produced on a non-blocking side stream immediately before the submit, no host
+    # synchronisation in between: the decode must still see them (it waits for that stream on the
+    # device), and work queued behind stream_wait_decode must not overtake the decode
+    import torch
+    from openfish_b200 import synth
+    of = native_lib
+    sl, T, N = 4, 400, 24
+    base = torch.from_numpy(synth.make_scores(T, N, sl, 141)).cuda()
+    want = of.decode_gpu(base, sl)
+    gb = of.gpubuf_init(T, N, sl)
+    side = torch.cuda.Stream()  # non-blocking with respect to the legacy default stream
+    out = [torch.zeros((N, T), dtype=torch.uint8).pin_memory() for _ in range(3)]
+    big = torch.empty((64, 1024, 1024), device="cuda")
+    torch.cuda.synchronize()
+    for _ in range(3):
+        sc = torch.zeros_like(base)
+        torch.cuda.synchronize()
+        with torch.cuda.stream(side):
+            for _ in range(20):          # a few milliseconds of work ahead of the producer
+                big.normal_()
+            sc.copy_(base)               # the scores appear late, on the side stream
+            of.decode_into(sc, sl, gb, *out, wait=False, stream=side)
+            of.stream_wait_decode(side, gb)
+            sc.zero_()                   # queued behind the decode: must not reach it
+        of.decode_wait(gb)
+        for k, o in zip(("moves", "sequence", "qstring"), out):
+            assert np.array_equal(o.numpy(), want[k]), k
+    side.synchronize()
+    assert float(sc.abs().max()) == 0.0
+    gb.free()
+
+
+def test_a_wait_that_runs_out_reaches_the_host_as_an_error(native_lib):
+    # one block waits 1 ms for a barrier nothing completes; the kernel returns, the host reports
+    # ERR_DEVICE_WAIT through the same code as a decode's completion, and the gpubuf is fine after
+    import torch
+    from openfish_b200 import synth
+    of = native_lib
+    sc = torch.from_numpy(synth.make_scores(150, 4, 3, 151)).cuda()
+    gb = of.gpubuf_init(150, 4, 3)
+    before = of.decode_gpu(sc, 3, gpubuf=gb)
+    assert of.selfcheck_wait(gb, 1000) == 7      # OPENFISH_B200_ERR_DEVICE_WAIT
+    assert of.selfcheck_wait(gb, 200) == 7       # and again: the status word was cleared in between
+    after = of.decode_gpu(sc, 3, gpubuf=gb)
+    for k in before:
+        assert np.array_equal(before[k], after[k])
+    gb.free()
+
+
 def test_argument_errors(native_lib):
     import torch
     of = native_lib
