@@ -14,6 +14,11 @@ same metric through openfish_decode_gpu with the scores starting in (page-locked
 and the results ending in host memory.  `roofline` describes the kernel that takes the most
 device time; `cpu_baseline` is the reference CPU decoder on this box's host cores on a bounded
 sample.  One JSON line is printed by rank 0.
+
+Outside the timed region the line also carries: `parity_spot_check` (every rank compares the
+first chunks of its shard with the CPU oracle, so that every GPU's output gets checked, not only
+the first one's), `config3_strong` (4096 chunks in all, split evenly over the ranks: strong
+scaling) and, on one GPU, `other_models` (the 1024-state and the 64-state model).
 """
 import argparse
 import json
@@ -44,9 +49,21 @@ CONFIG = {"workload": WORKLOAD,
 # moves, sequence, qstring written)
 B_KERNEL = {"bwd_scan": T * 4 * NS * 2 + (T + 1) * NS * 4,              # scores in, bwd out
             "fwd_scan": T * 4 * NS * 2 + 2 * (T + 1) * NS * 4,          # scores, bwd in; post out (forward scan + posterior)
-            "beam_search": T * 4 * NS * 2 + (T + 1) * NS * 4 + 32 * (T + 1),  # scores, bwd in; back-pointers out
+            # what the search needs: <= 128 fp16 scores and <= 160 fp32 backward scores gathered per
+            # timestep, one back-pointer byte per slot out (the rows it streams to find them are
+            # traffic, not algorithmic bytes)
+            "beam_search": T * (128 * 2 + 160 * 4) + 32 * (T + 1),
             "posterior_seq": 32 * (T + 1) + 9 * 4 * T + 3 * T}          # back-pointers, <= 9 posteriors per step in; results out
-B_CHUNK = 2 * T * 4 * NS * 2 + 3 * (T + 1) * NS * 4 + 3 * T
+
+
+def chunk_bytes(state_len, t):
+    """Algorithmic bytes of one chunk's decode: scores read once per scan; bwd written then read;
+    post, moves, sequence, qstring written."""
+    ns = 4 ** state_len
+    return 2 * t * 4 * ns * 2 + 3 * (t + 1) * ns * 4 + 3 * t
+
+
+B_CHUNK = chunk_bytes(STATE_LEN, T)
 
 
 def measured_peak():
@@ -216,16 +233,81 @@ def run_reference(args, rank, world):
         times.append(dt)
     total = sum(times)
     value = n * len(times) / total
+    config = dict(CONFIG, workload=WORKLOAD + "; this arm decodes a %d-chunk sample of it per step (the CPU "
+                  "decoder works chunk by chunk, so its chunks/s does not depend on the batch size)" % n)
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32 storage, f64 exp/log (the CPU decoder's arithmetic)", "data": "synthetic",
-            "config": CONFIG, "sample_chunks_per_step": n,
+            "config": config, "sample_chunks_per_step": n,
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": min(cores, n), "kind": kind,
                              "sample": "%d chunks of the workload per step, openfish_decode_cpu with %d threads" % (n, min(cores, n))},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
+
+
+def timed_decodes(of, scores, state_len, steps, warmup=3):
+    """Median device time (the library's own CUDA events) of `steps` decodes of a resident batch,
+    after `warmup` untimed ones; also the decoded bases of the batch."""
+    import torch
+    t, n, _ = scores.shape
+    gb = of.gpubuf_init(t, n, state_len)
+    res = [torch.empty((n, t), dtype=torch.uint8).pin_memory() for _ in range(3)]
+    ms = []
+    for k in range(warmup + steps):
+        of.decode_into(scores, state_len, gb, *res)
+        if k >= warmup:
+            ms.append(gb.last_decode_ms())
+    gb.free()
+    med = {k: statistics.median(m[k] for m in ms) for k in ms[0]}
+    return med, float(res[0].sum())
+
+
+def other_model(of, dev, state_len, t, n, seed, peak):
+    """One more model/shape with the same kernels, scores resident: ms per decode, chunks/s and the
+    whole-decode roofline on that shape's own algorithmic bytes."""
+    from openfish_b200 import synth
+    scores = synth.make_scores_device(t, n, state_len, seed, dev)
+    med, bases = timed_decodes(of, scores, state_len, steps=5)
+    del scores
+    gbs = chunk_bytes(state_len, t) * n / (med["total"] * 1e-3) / 1e9
+    return {"state_len": state_len, "T": t, "N": n, "ms_per_decode": med["total"],
+            "chunks_per_sec": n / (med["total"] * 1e-3), "bases_per_sec": bases / (med["total"] * 1e-3),
+            "kernel_ms": {k: med[k] for k in ("bwd_scan", "fwd_scan", "beam_search", "posterior_seq", "d2h")},
+            "roofline_whole_decode": {"achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                                      "algorithmic_bytes_per_chunk": chunk_bytes(state_len, t)}}
+
+
+def spot_check(of, scores, results, state_len, n_check):
+    """The first n_check chunks of this rank's batch through the CPU oracle (the checker, outside
+    every timed region): how many have moves and sequence identical to what the GPU returned."""
+    import numpy as np
+    import oracle
+    sub = scores[:, :n_check, :].float().cpu().numpy()
+    ref = oracle.decode(np.ascontiguousarray(sub), state_len, None, min(n_check, os.cpu_count() or 1))
+    same = 0
+    for c in range(n_check):
+        same += int(np.array_equal(results[0][c].numpy(), ref["moves"][c])
+                    and np.array_equal(results[1][c].numpy(), ref["sequence"][c]))
+    return same
+
+
+def reference_cuda():
+    """The reference's own CUDA kernels (generic code, compiled for sm_100a by baseline/Makefile)
+    timed on this GPU by a child process; None of this library's code runs there, and nothing of
+    the reference's runs in this process."""
+    import subprocess
+    script = os.path.join(ROOT, "baseline", "time_reference_cuda.py")
+    try:
+        r = subprocess.run([sys.executable, script], capture_output=True, text=True, timeout=300)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": "the reference's CUDA path did not finish within 300 s"}
+    lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+    if r.returncode != 0 or not lines:
+        tail = (r.stderr or "").strip().splitlines()[-1:] or [""]
+        return {"unavailable": "the reference's CUDA path ended with code %d: %s" % (r.returncode, tail[0][:200])}
+    return json.loads(lines[-1])
 
 
 def main():
@@ -235,6 +317,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-reference-cuda", action="store_true")
+    ap.add_argument("--profile", type=int, metavar="CHUNKS", default=0,
+                    help="for captures under a profiler: decode CHUNKS chunks --warmup + --steps times, nothing else")
+    ap.add_argument("--profile-model", type=int, default=STATE_LEN, help="state_len of the --profile decode (3, 4 or 5)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -257,10 +343,18 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
+    if args.profile:
+        # the same decode call on a smaller batch, so that a profiler's capture stays small
+        sl = args.profile_model
+        sc = synth.make_scores_device(T, args.profile, sl, SEED, dev)
+        med, _ = timed_decodes(of, sc, sl, steps=args.steps, warmup=args.warmup)
+        print(json.dumps({"profile_chunks": args.profile, "state_len": sl, "T": T, "ms": med}), flush=True)
+        return
+
     # this rank's shard: chunks [rank*512, (rank+1)*512) of the job, generated in its own HBM
     lo, hi = sharding.shard_range(N_PER_GPU * world, rank, world)
     n_local = hi - lo
-    scores = synth.make_scores_device(T, n_local, STATE_LEN, SEED + rank, dev)
+    scores = synth.make_scores_device(T, n_local, STATE_LEN, SEED, dev, first_chunk=lo)
     gb = of.gpubuf_init(T, n_local, STATE_LEN)
     res = [torch.empty((n_local, T), dtype=torch.uint8).pin_memory() for _ in range(3)]
 
@@ -369,6 +463,41 @@ def main():
         api_wall.append(1e3 * (time.perf_counter() - a0))
     rotary = measure_rotary(of, dev, cpu_too=(world == 1 and not args.no_cpu_baseline)) if rank == 0 else None
 
+    # ---- outside the timed regions ---------------------------------------------------------
+    # every rank checks the head of its own shard against the oracle: the last timed decode's
+    # results are still in `res`
+    of.decode_into(scores, STATE_LEN, gb, *res)
+    n_check = min(8, n_local)
+    same = spot_check(of, scores, res, STATE_LEN, n_check)
+    checked_total = sharding.sum_over_ranks(float(n_check), dev if world > 1 else None)
+    same_total = sharding.sum_over_ranks(float(same), dev if world > 1 else None)
+    gb.free()
+    h2d_bytes = int(scores.numel() * 2)
+    del scores, d_ins, h_scores
+    torch.cuda.empty_cache()
+
+    # BASELINE configuration 3 as written: 4096 chunks in all, split evenly by chunk index (strong
+    # scaling; on one GPU all 4096, 14 GB of scores)
+    n_strong = 4096
+    s_lo, s_hi = sharding.shard_range(n_strong, rank, world)
+    sc3 = synth.make_scores_device(T, s_hi - s_lo, STATE_LEN, SEED, dev, first_chunk=s_lo)
+    barrier()
+    med3, bases3 = timed_decodes(of, sc3, STATE_LEN, steps=3, warmup=3)
+    del sc3
+    torch.cuda.empty_cache()
+    strong_ms = sharding.max_over_ranks(med3["total"], dev if world > 1 else None)
+    strong_bases = sharding.sum_over_ranks(bases3, dev if world > 1 else None)
+    peak_gbs, _ = measured_peak()
+    config3 = {"chunks_total": n_strong, "chunks_per_gpu": s_hi - s_lo, "ms_per_decode": strong_ms,
+               "chunks_per_sec": n_strong / (strong_ms * 1e-3), "bases_per_sec": strong_bases / (strong_ms * 1e-3),
+               "per_gpu_hbm_gbs": B_CHUNK * (s_hi - s_lo) / (strong_ms * 1e-3) / 1e9,
+               "scaling": "strong", "timing": "median of 3 decodes after 3 warm-ups, library CUDA events, max over ranks"}
+    others = None
+    if world == 1:
+        others = [other_model(of, dev, 5, 1666, 256, 0x0F17, peak_gbs),
+                  other_model(of, dev, 3, 1000, 16, 0x0F15, peak_gbs),
+                  other_model(of, dev, 3, 1666, 1024, 0x0F15, peak_gbs)]
+
     if rank == 0:
         peak, peak_src = measured_peak()
         per = {k: v / args.steps for k, v in ms.items()}
@@ -400,7 +529,7 @@ def main():
             "roofline_whole_decode": {"achieved": whole, "peak": peak, "unit": "GB/s", "frac": whole / peak,
                                       "algorithmic_bytes_per_chunk": B_CHUNK,
                                       "frac_of_nominal_8000_gbs": whole / 8000.0},
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(scores.numel() * 2),
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes,
                     "d2h_bytes_per_step": int(3 * n_local * T), "steps": e2e_steps,
                     "call": "openfish_decode_gpu after a page-locked host-to-device copy of the scores; "
                             "two host threads alternate so that one's copy overlaps the other's decode"},
@@ -412,16 +541,28 @@ def main():
                               "note": "two gpubufs, the next decode submitted before the previous one is waited for"},
             "rotary": rotary,
             "clocks": clocks,
+            "parity_spot_check": {"chunks_checked": int(checked_total), "identical": int(same_total),
+                                  "what": "moves and sequence of the first %d chunks of every rank's shard against the CPU oracle" % n_check},
+            "config3_strong": config3,
+            "other_models": others,
         }
+        if world == 1 and not args.no_reference_cuda:
+            rc = reference_cuda()
+            if "decode_hac_N512" in rc:
+                rc["decode_hac_N512"]["this_library_ms"] = min(api_wall)
+                rc["decode_hac_N512"]["speedup_wall"] = rc["decode_hac_N512"]["wall_ms"] / min(api_wall)
+            if rc.get("rotary") and rotary:
+                rc["rotary"]["this_library_ms"] = rotary["ms"]
+                rc["rotary"]["speedup"] = rc["rotary"]["ms"] / rotary["ms"]
+            line["reference_cuda"] = rc
         if world == 1 and not args.no_cpu_baseline:
             cores = os.cpu_count() or 1
             n_s = min(N_PER_GPU, max(cores, 256))
-            sc32 = scores[:, :n_s, :].float().cpu().numpy()
+            sc32 = synth.make_scores_device(T, n_s, STATE_LEN, SEED, dev).float().cpu().numpy()
             rate, kind, dt = cpu_decode_rate(np.ascontiguousarray(sc32), cores)
             line["cpu_baseline"] = {"value": rate, "unit": UNIT, "cores": min(cores, n_s), "kind": kind,
                                     "sample": "first %d chunks of the same batch, one openfish_decode_cpu call, %.2f s" % (n_s, dt)}
         print(json.dumps(line), flush=True)
-    gb.free()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -136,8 +136,9 @@ int openfish_b200_kernels_per_decode(void);
  * malloc or other allocating routine.
  *
  *   - Shapes whose intermediates do not fit are refused with OPENFISH_B200_ERR_SCRATCH_LIMIT:
- *     needed = 3*N*(T+1)*4^state_len*4 + N*(T+1)*32 + N*T*28 bytes (+ 5 KB), e.g. fast T=1666 up
- *     to N=36, hac up to N=9, sup up to N=2.
+ *     needed = k*N*(T+1)*4^state_len*4 + N*(T+1)*32 + N*T*28 bytes (+ 5 KB) with k = 2 tensors
+ *     for state_len 4 and 5 (backward scores and posteriors) and 3 for state_len 3 (forward
+ *     scores as well), e.g. at T=1666 fast up to N=36, hac up to N=14, sup up to N=3.
  *   - All calls on one GPU share the array.  It keeps what the previous call left (the call
  *     clears what has to start from zero itself); two calls that overlap on the same GPU race,
  *     so serialise them.

@@ -15,6 +15,8 @@ LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libopenfish.so")
 CLI_SRC = os.path.join(HERE, "cli", "openfish_cli.c")
 CLI = os.path.join(HERE, "bin", "openfish")  # the command-line driver, linked against LIB
+CMP_SRC = os.path.join(HERE, "cli", "compare_blob.c")
+CMP = os.path.join(HERE, "bin", "compare_blob")  # tensor-file comparison in the reference's format
 CU = ["scan.cu", "beam_search.cu", "posterior_seq.cu", "rotary.cu", "decode_b200.cu", "decode_static.cu",
       "selfcheck.cu"]
 CC = ["openfish_api.c"]
@@ -24,10 +26,10 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
 
 
 def _stale():
-    if not os.path.exists(LIB) or not os.path.exists(CLI):
+    if not os.path.exists(LIB) or not os.path.exists(CLI) or not os.path.exists(CMP):
         return True
-    t = min(os.path.getmtime(LIB), os.path.getmtime(CLI))
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [CLI_SRC]
+    t = min(os.path.getmtime(LIB), os.path.getmtime(CLI), os.path.getmtime(CMP))
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [CLI_SRC, CMP_SRC]
     deps += [os.path.join(dp, f) for dp, _, fs in os.walk(os.path.join(ROOT, "include")) for f in fs]
     return any(os.path.getmtime(d) > t for d in deps)
 
@@ -59,6 +61,7 @@ def build(force=False, verbose=False):
     os.makedirs(os.path.dirname(CLI), exist_ok=True)
     subprocess.run(["gcc", "-O2", "-Wall", "-std=gnu11", "-I", os.path.join(ROOT, "include"), CLI_SRC, "-o", CLI,
                     "-L", LIB_DIR, "-lopenfish", "-Wl,-rpath,$ORIGIN/../lib", "-lm"], check=True)
+    subprocess.run(["gcc", "-O2", "-Wall", "-std=gnu11", CMP_SRC, "-o", CMP, "-lm"], check=True)
     return LIB
 
 

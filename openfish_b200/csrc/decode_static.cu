@@ -6,7 +6,7 @@
 // device-wide synchronisation a cudaMalloc / cudaFree implies in the middle of its steady
 // state.  openfish_gpubuf_init does ten cudaMallocs, a cudaMallocHost, a stream and four events,
 // and openfish_decode_gpu three host mallocs per call.  The entry point below needs none of
-// that: every intermediate of the decode (backward and forward scores, posteriors, back-pointers, path
+// that: every intermediate of the decode (backward scores, posteriors, back-pointers, path
 // states, per-timestep qualities, the arithmetic tables, the status word) lives in ONE
 // file-scope device array of fixed size, the results go to device buffers the caller owns, the
 // work runs on the legacy default stream, and the only runtime calls are kernel launches,
@@ -96,12 +96,14 @@ extern "C" int openfish_b200_decode_static(int T, int N, int C, const void *scor
         return report(OPENFISH_B200_ERR_OPTION, "beam_width must be 32");
 
     // carve the array: tables | status | bwd | fwd | post | back-pointers | states | qual | probs
+    // (no forward tensor for the models whose forward scan forms the posterior itself)
+    const bool fused = of_forward_posterior_fused(state_len);
     const size_t nt = (size_t)N * T, rows = (size_t)N * (T + 1);
     size_t off = 0;
     const size_t o_tables = off; off += align_up(sizeof(ofx::Tables));
     const size_t o_status = off; off += 256;
     const size_t o_bwd = off; off += align_up(rows * ns * sizeof(float));
-    const size_t o_fwd = off; off += align_up(rows * ns * sizeof(float));
+    const size_t o_fwd = off; off += fused ? 0 : align_up(rows * ns * sizeof(float));
     const size_t o_post = off; off += align_up(rows * ns * sizeof(float));
     const size_t o_bp = off; off += align_up(rows * 32);
     const size_t o_init = off; off += align_up((size_t)N * 32 * sizeof(int));
@@ -128,18 +130,22 @@ extern "C" int openfish_b200_decode_static(int T, int N, int C, const void *scor
     const ofx::Tables *tables = reinterpret_cast<const ofx::Tables *>(base + o_tables);
     int *status = reinterpret_cast<int *>(base + o_status);
     float *bwd = reinterpret_cast<float *>(base + o_bwd);
-    float *fwd = reinterpret_cast<float *>(base + o_fwd);
+    float *fwd = fused ? nullptr : reinterpret_cast<float *>(base + o_fwd);
+    float *post = reinterpret_cast<float *>(base + o_post);
     cudaStream_t stream = 0;  // legacy default stream: nothing to create
     e = cudaMemsetAsync(status, 0, sizeof(int), stream);  // the one thing that must start at zero
     if (e == cudaSuccess)
         e = of_launch_scans(scores_TNC, bwd, fwd, T, N, state_len, options->blank_score, tables,
                             status, ofd::kDefaultWaitLimitNs, stream);
+    if (e == cudaSuccess && fused)
+        e = of_launch_forward_posterior(scores_TNC, bwd, post, T, N, state_len, options->blank_score,
+                                        tables, status, ofd::kDefaultWaitLimitNs, stream);
     if (e == cudaSuccess) {
         OfDecodeArgs a;
         a.scores = static_cast<const __half *>(scores_TNC);
         a.bwd = bwd;
         a.fwd = fwd;
-        a.post = reinterpret_cast<float *>(base + o_post);
+        a.post = post;
         a.bp = base + o_bp;
         a.init_kmers = reinterpret_cast<int *>(base + o_init);
         a.moves = moves_gpu;

@@ -103,29 +103,6 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
         : "memory");
 }
 
-// Named barriers (ids 1..15; 0 is __syncthreads): N threads (a multiple of 32) take part in each
-// round, some of which may only announce themselves (arrive) and carry on.  Ids and counts are
-// compile-time constants so that a kernel reserves only the barriers it names.
-template <int ID, int N>
-__device__ __forceinline__ void named_bar_sync() {
-    asm volatile("bar.sync %0, %1;" ::"n"(ID), "n"(N) : "memory");
-}
-template <int ID, int N>
-__device__ __forceinline__ void named_bar_arrive() {
-    asm volatile("bar.arrive %0, %1;" ::"n"(ID), "n"(N) : "memory");
-}
-// the same for a pair of barriers ID, ID + 1 picked at run time
-template <int ID, int N>
-__device__ __forceinline__ void named_bar_sync2(int which) {
-    if (which) named_bar_sync<ID + 1, N>();
-    else named_bar_sync<ID, N>();
-}
-template <int ID, int N>
-__device__ __forceinline__ void named_bar_arrive2(int which) {
-    if (which) named_bar_arrive<ID + 1, N>();
-    else named_bar_arrive<ID, N>();
-}
-
 // Order-preserving map float -> int32 (and back) so integer warp reductions can take a max.
 __device__ __forceinline__ int float_order_key(float f) {
     const int i = __float_as_int(f);

@@ -336,39 +336,36 @@ __device__ __forceinline__ void scan_body(unsigned char *smem_raw, int block, co
 //
 // In the plain variant a state whose rounding the fp32 evaluation cannot certify sends its whole
 // warp through the value-exact routine before the timestep can end, and almost every timestep
-// has a few such states: the exact routine's latency (a chain of some thirty dependent FP64
-// operations, close to a thousand cycles) is paid on nearly every step.  Here the scan warps
-// never wait for it.  An uncertified state gets the likelier of its two candidate floats and is
-// put on a list; two checker warps, taking the timesteps in turn, recompute the listed states
-// exactly while the scan warps run on, and each has two timesteps for it: the verdict on the
-// guesses of timestep d is looked at when timestep d+2 has ended.  Nearly always every guess was
-// right and nothing else happens.  When one was wrong (one timestep in seventeen with 256
-// states) the checker has put the right value in place and the scan warps go back and redo
-// timesteps d+1 and d+2 from it; what the other checker was doing meanwhile is thrown away.
-// What reaches HBM is, value for value, what the exact routine alone would have produced.
-//
-// Who waits for whom.  The warps that walk the timesteps (scan warps; with the posterior on top
-// also the posterior warp) meet at one named barrier per timestep; the checkers are not part of
-// it.  Work goes to checker k through barrier kBarWork + k (the walkers only arrive, the checker
-// waits), verdicts come back through kBarDone + k (the checker only arrives).  Four row buffers
-// rotate: while timestep i writes row i+1, row i is its input, row i-1 is the input a redo would
-// start from and the guesses under check, and row i-2 is the input of that check.  A score row
-// stays in the ring until the verdict on its timestep has been looked at.
+// has a few such states: the exact routine's latency is paid on nearly every step.  Here the
+// scan warps do not wait for it.  An uncertified state gets the likelier of its two candidate
+// floats and is put on a list; while the scan warps work on the next timestep, a checker warp
+// recomputes the listed states exactly.  If every guess was right (about three timesteps in
+// four) nothing else happens.  If one was wrong the block pauses at the end of that next
+// timestep: the checker corrects the value and recomputes exactly the five states of the next
+// row that read it (the state itself and its four readers) before anybody reads those, and the
+// scan carries on.  (Letting the scan run on and chasing the consequences a step behind does
+// not work: a one-ulp change of an input moves an output by one ulp with a probability equal to
+// that input's weight in the sum, and the weights of a state over its five readers add up to
+// about one, so corrections would breed as fast as they die.)  What reaches HBM is, value for
+// value, what the exact routine alone would have produced.  Three row buffers rotate so that the
+// inputs of a timestep are still there while it is being checked, and score rows are released
+// one timestep late.
 template <int NS, int SPT, int RING>
 struct SpecSmem {
     static constexpr int kRowBytes = NS * 4 * 2;
     static constexpr int NW = NS / SPT / 32;  // scan warps
     static constexpr int kPerWarp = 16;       // listed states per warp and timestep, at most
     alignas(128) unsigned char ring[RING][kRowBytes];
-    alignas(16) float alpha[4][NS];
+    alignas(16) float alpha[3][NS];
     alignas(16) double exp2_rep[ofx::kExpTab * kExpCopies];
     double rcp_c[ofx::kLogTab];
     double log_c[ofx::kLogTab];
     alignas(8) uint64_t full[RING];
-    unsigned short listed[4][NW][kPerWarp];
-    int n_listed[4][NW];
-    int n_wrong[2];    // per checker: wrong guesses in the timestep it has just checked
-    int work_step[2];  // per checker: the timestep handed to it, -1 = no more work
+    unsigned short listed[2][NW][kPerWarp];
+    int n_listed[2][NW];
+    int n_wrong[2];
+    unsigned short wrong_state[NW * kPerWarp];
+    float wrong_value[NW * kPerWarp];
     // settle-now path: a warp's uncertified states, dealt out to its lanes, and their exact values
     unsigned short redo_state[NW][32 * SPT];
     float redo_value[NW][32 * SPT];
@@ -376,12 +373,12 @@ struct SpecSmem {
 };
 
 //
-// POST (forward direction only): the rows are not written out; one more warp turns each row, once
-// it is final, into the posterior row  softmax_s(fwd[t][s] + bwd[t][s])  and writes that (`out`
-// is then the posterior tensor and `bwd_in` the finished backward scores).  Row r is final once
-// the verdict on timestep r-1 has been looked at, which happens at the end of timestep r+1, and its
-// buffer is written again during timestep r+3, so the posterior warp takes it during timestep
-// r+2; the last rows are taken after the scan.  The arithmetic is that of the stand-alone
+// POST (forward direction only): the rows are not written out; a fourth kind of warp turns each
+// row, once it is final, into the posterior row  softmax_s(fwd[t][s] + bwd[t][s])  and writes
+// that (`out` is then the posterior tensor and `bwd_in` the finished backward scores).  Row r is
+// final after the barrier that ends timestep r (its guesses have been checked by then) and its
+// buffer is written again during timestep r+2, so the posterior warp takes it during timestep
+// r+1; the last two rows are taken after the scan.  The arithmetic is that of the stand-alone
 // posterior loop in posterior_seq.cu, operation for operation.
 template <class Topo, int NS, int SPT, int RING, bool POST>
 __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, const __half *scores,
@@ -393,7 +390,6 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
     constexpr int NW = Smem::NW, PER = Smem::kPerWarp;
     static_assert(!POST || Topo::kForward, "the posterior rides on the forward scan");
     static_assert(TPC % 32 == 0, "scan warps must be full");
-    static_assert((RING & (RING - 1)) == 0, "ring slots are found by masking");
     Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -403,12 +399,11 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
         sm.rcp_c[i] = tables->rcp_c[i];
         sm.log_c[i] = tables->log_c[i];
     }
-    for (int i = tid; i < 4 * NW; i += blockDim.x) (&sm.n_listed[0][0])[i] = 0;
+    for (int i = tid; i < 2 * NW; i += blockDim.x) (&sm.n_listed[0][0])[i] = 0;
     for (int i = tid; i < NS; i += blockDim.x) sm.alpha[0][i] = 0.f;
     if (tid == 0) {
         sm.abort_flag = 0;
         sm.n_wrong[0] = sm.n_wrong[1] = 0;
-        sm.work_step[0] = sm.work_step[1] = -1;
         for (int r = 0; r < RING; ++r) ofd::mbar_init(&sm.full[r], 1);
         ofd::mbar_fence_init();
     }
@@ -419,101 +414,164 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
     float *out_chunk = out + (size_t)chunk * (size_t)(T + 1) * NS;
     const ofx::TabRef tr = {sm.exp2_rep + (tid & (kExpCopies - 1)), kExpCopies, sm.rcp_c, sm.log_c};
 
-    // warps: NW scan warps, two checkers, and with POST the posterior warp
-    constexpr int kChecker0 = NW, kPostWarp = NW + 2;
-    constexpr int kWalkers = (NW + (POST ? 1 : 0)) * 32;  // threads that walk the timesteps
-    enum { kBarStep = 1, kBarWork = 2, kBarDone = 4 };    // named barriers (0 is __syncthreads)
+    if (warp == NW) {
+        // ------------------------------------------------------------------ copy warp
+        // A slot is refilled one timestep late: the checker still reads the scores of the
+        // timestep it is checking.
+        const bool issuer = lane == 0;
+        int issued = 0;  // copies go out in row order; after an abort no more are issued
+        auto fill = [&](int i) {
+            if (sm.abort_flag) return;
+            const int slot = i % RING;
+            ofd::mbar_arrive_expect_tx(&sm.full[slot], Smem::kRowBytes);
+            ofd::bulk_g2s(sm.ring[slot], chunk_scores + t_stride * (size_t)Topo::score_row(i, T), Smem::kRowBytes,
+                          &sm.full[slot]);
+            ++issued;
+        };
+        auto landed = [&](int i) {
+            ofd::mbar_wait_bounded(&sm.full[i % RING], (uint32_t)(i / RING) & 1u, &sm.abort_flag, status, wait_ns);
+        };
+        if (issuer) {
+            for (int i = 0; i < RING && i < T; ++i) fill(i);
+            if (T > 0) landed(0);
+        }
+        __syncthreads();
+        for (int i = 0; i < T; ++i) {
+            if (issuer && i + 1 < T) landed(i + 1);
+            __syncthreads();
+            if (sm.n_wrong[i & 1]) __syncthreads();
+            if (issuer && i >= 1 && i - 1 + RING < T) fill(i - 1 + RING);
+        }
+        if (POST) __syncthreads();  // the last row is final
+        // after an abort the newest copies get a bounded chance to land before the block retires
+        if (issuer && sm.abort_flag) ofd::mbar_drain_bounded(sm.full, RING, issued, wait_ns);
+        return;
+    }
 
-    if (warp == kChecker0 || warp == kChecker0 + 1) {
-        // ------------------------------------------------------------------ checker warps
-        const int k = warp - kChecker0;
-        for (;;) {
-            ofd::named_bar_sync2<kBarWork, kWalkers + 32>(k);
-            const int t = *(volatile int *)&sm.work_step[k];
-            if (t < 0) break;
-            // the states listed during timestep t: inputs row t, scores in slot t % RING, guesses
-            // in row t+1 (and, without POST, in the output row of timestep t)
-            const float *in = sm.alpha[t & 3];
-            float *guess = sm.alpha[(t + 1) & 3];
-            float *out_row = out_chunk + (size_t)Topo::out_row(t, T) * NS;
-            const unsigned char *row = sm.ring[t & (RING - 1)];
-            int total = 0, nw = 0;
-#pragma unroll
-            for (int w = 0; w < NW; ++w) total += sm.n_listed[t & 3][w];
-            for (int base = 0; base < total; base += 32) {
-                const int e = base + lane;
-                int s = 0, acc = 0;
-#pragma unroll
-                for (int w = 0; w < NW; ++w) {
-                    const int c = sm.n_listed[t & 3][w];
-                    if (e >= acc && e < acc + c) s = sm.listed[t & 3][w][e - acc];
-                    acc += c;
-                }
-                float v[5];
-                terms_of<Topo>(s, in, row, stay, v);
-                const float x = ofx::lse5_exact(v, tr);
-                const bool wrong = e < total && __float_as_uint(x) != __float_as_uint(guess[s]);
-                if (wrong) {
-                    guess[s] = x;
-                    if (!POST) out_row[s] = x;
-                }
-                nw += __popc(__ballot_sync(0xffffffffu, wrong));
+    if (POST && warp == NW + 2) {
+        // ------------------------------------------------------------------ posterior warp
+        const float *bwd_chunk = bwd_in + (size_t)chunk * (size_t)(T + 1) * NS;
+        const float m0 = PosteriorRow<NS>::row_max(bwd_chunk, lane);
+        PosteriorRow<NS> pr;
+        auto fetch = [&](int r) { pr.fetch(bwd_chunk + (size_t)r * NS, lane); };
+        auto emit = [&](int r) { pr.emit(sm.alpha[r % 3], out_chunk + (size_t)r * NS, m0, lane); };
+        fetch(0);
+        __syncthreads();  // start of the scan
+        int next_row = 0;
+        for (int i = 0; i < T; ++i) {
+            // during timestep i the rows up to i-1 are final (and row 0 always is)
+            if (next_row == 0 || next_row <= i - 1) {
+                emit(next_row);
+                ++next_row;
+                fetch(next_row);  // next_row <= T
             }
-            if (lane == 0) sm.n_wrong[k] = nw;
-            __threadfence_block();
-            ofd::named_bar_arrive2<kBarDone, kWalkers + 32>(k);
+            __syncthreads();
+            if (sm.n_wrong[i & 1]) __syncthreads();
+        }
+        while (next_row <= T - 1) {  // final since the last timestep's barrier
+            emit(next_row);
+            ++next_row;
+            fetch(next_row);
+        }
+        __syncthreads();  // the last row is final
+        emit(T);
+        return;
+    }
+
+    if (warp == NW + 1) {
+        // ------------------------------------------------------------------ checker warp
+        __syncthreads();  // start of the scan
+        for (int i = 0; i <= T; ++i) {
+            // During timestep i (for i = T: after the last one) check the states listed during
+            // timestep i-1: inputs alpha[(i-1)%3], scores in slot (i-1)%RING, guesses in
+            // alpha[i%3] and in the output row of timestep i-1.
+            int nw = 0;
+            if (i >= 1) {
+                const int par = (i - 1) & 1;
+                int total = 0;
+#pragma unroll
+                for (int w = 0; w < NW; ++w) total += sm.n_listed[par][w];
+                for (int base = 0; base < total; base += 32) {
+                    const int e = base + lane;
+                    int s = 0, acc = 0;
+#pragma unroll
+                    for (int w = 0; w < NW; ++w) {
+                        const int c = sm.n_listed[par][w];
+                        if (e >= acc && e < acc + c) s = sm.listed[par][w][e - acc];
+                        acc += c;
+                    }
+                    float v[5];
+                    terms_of<Topo>(s, sm.alpha[(i - 1) % 3], sm.ring[(i - 1) % RING], stay, v);
+                    const float x = ofx::lse5_exact(v, tr);
+                    const bool wrong = e < total && __float_as_uint(x) != __float_as_uint(sm.alpha[i % 3][s]);
+                    const uint32_t wm = __ballot_sync(0xffffffffu, wrong);
+                    if (wrong) {
+                        const int at = nw + __popc(wm & ((1u << lane) - 1u));
+                        sm.wrong_state[at] = (unsigned short)s;
+                        sm.wrong_value[at] = x;
+                    }
+                    nw += __popc(wm);
+                }
+                __syncwarp();
+            }
+            if (i == T) {
+                // the last row: no timestep reads it any more, just correct it
+                if (POST) {
+                    for (int e = lane; e < nw; e += 32) sm.alpha[T % 3][sm.wrong_state[e]] = sm.wrong_value[e];
+                    __syncthreads();  // the last row is final
+                } else {
+                    float *row = out_chunk + (size_t)Topo::out_row(T - 1, T) * NS;
+                    for (int e = lane; e < nw; e += 32) row[sm.wrong_state[e]] = sm.wrong_value[e];
+                }
+                break;
+            }
+            if (lane == 0) sm.n_wrong[i & 1] = nw;
+            __syncthreads();  // end of timestep i
+            if (nw) {
+                float *prev_row = out_chunk + (size_t)Topo::out_row(i - 1, T) * NS;
+                for (int e = lane; e < nw; e += 32) {
+                    const int s = sm.wrong_state[e];
+                    sm.alpha[i % 3][s] = sm.wrong_value[e];
+                    if (!POST) prev_row[s] = sm.wrong_value[e];
+                }
+                __syncwarp();
+                // the five states of timestep i's row that read a corrected value
+                float *this_row = out_chunk + (size_t)Topo::out_row(i, T) * NS;
+                for (int idx = lane; idx < 5 * nw; idx += 32) {
+                    const int s = sm.wrong_state[idx / 5], d = idx % 5;
+                    const int dep = d == 4 ? s : Topo::reader(s, d);
+                    float v[5];
+                    terms_of<Topo>(dep, sm.alpha[i % 3], sm.ring[i % RING], stay, v);
+                    float x;  // certified fp32 evaluation first: it settles all but about 1 in 100
+                    if (!ofd::lse5_try_fast(v, x)) x = ofx::lse5_exact(v, tr);
+                    sm.alpha[(i + 1) % 3][dep] = x;
+                    if (!POST) this_row[dep] = x;
+                }
+                __syncthreads();  // corrections in place
+            }
         }
         return;
     }
 
-    // ---------------------------------------------------------------------- the walkers
-    // One lane among them keeps the score ring full: the posterior warp's first lane, or without
-    // that warp the first scan warp's.  Row i goes into slot i % RING.
-    const bool copies = lane == 0 && warp == (POST ? kPostWarp : 0);
-    int issued = 0;  // (the copying lane's count; copies go out in row order, none after an abort)
-    auto fill = [&](int i) {
-        if (sm.abort_flag) return;
-        const int slot = i & (RING - 1);
-        ofd::mbar_arrive_expect_tx(&sm.full[slot], Smem::kRowBytes);
-        ofd::bulk_g2s(sm.ring[slot], chunk_scores + t_stride * (size_t)Topo::score_row(i, T), Smem::kRowBytes,
-                      &sm.full[slot]);
-        ++issued;
-    };
-    auto landed = [&](int i) {
-        ofd::mbar_wait_bounded(&sm.full[i & (RING - 1)], (uint32_t)(i / RING) & 1u, &sm.abort_flag, status, wait_ns);
-    };
-    if (copies) {
-        for (int i = 0; i < RING && i < T; ++i) fill(i);
-        if (T > 0) landed(0);
-    }
-
-    const bool scans = warp < NW;
+    // ---------------------------------------------------------------------- scan warps
     const int j = tid % NJ;
     const int k0 = (tid / NJ) * SPT;
-    const uint32_t lt_mask = (1u << lane) - 1u;
-    float res[SPT];  // (scan warps) the thread's states of the current row: its stay terms for the next timestep
-#pragma unroll
-    for (int k = 0; k < SPT; ++k) res[k] = 0.f;
-    if (scans && !POST) {
+    if (!POST) {
 #pragma unroll
         for (int k = 0; k < SPT; ++k) out_chunk[(size_t)Topo::zero_row(T) * NS + Topo::state(j, k0 + k)] = 0.f;
     }
-    // (posterior warp)
-    PosteriorRow<NS> pr;
-    float m0 = 0.f;
-    int next_row = 0;
-    const float *bwd_chunk = POST ? bwd_in + (size_t)chunk * (size_t)(T + 1) * NS : nullptr;
-    if (POST && !scans) {
-        m0 = PosteriorRow<NS>::row_max(bwd_chunk, lane);
-        pr.fetch(bwd_chunk, lane);
-    }
-    ofd::named_bar_sync<kBarStep, kWalkers>();  // the first score row is there
-
-    // One timestep of a scan warp: row i (and score row i) in, row i+1 out, uncertified states listed.
-    auto scan_step = [&](int i) {
-        const float *in = sm.alpha[i & 3];
-        float *nxt = sm.alpha[(i + 1) & 3];
-        const unsigned char *row = sm.ring[i & (RING - 1)];
+    __syncthreads();
+    const uint32_t lt_mask = (1u << lane) - 1u;
+    float res[SPT];  // the thread's states of the current row: its stay terms for the next timestep
+#pragma unroll
+    for (int k = 0; k < SPT; ++k) res[k] = 0.f;
+    // rotating pointers instead of i % 3 and i % RING: row i is read from `in`, row i+1 goes to `nxt`
+    const float *in = sm.alpha[0];
+    float *nxt = sm.alpha[1], *spare = sm.alpha[2];
+    const unsigned char *row = sm.ring[0];
+    float *gmem_out = out_chunk + (size_t)Topo::out_row(0, T) * NS;
+    const ptrdiff_t gmem_step = Topo::kForward ? (ptrdiff_t)NS : -(ptrdiff_t)NS;
+    for (int i = 0; i < T; ++i) {
         float v[SPT][5];
         bool ok[SPT];
         thread_terms<Topo, SPT>(in, row, j, k0, stay, v, res);
@@ -565,75 +623,26 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
             int base = 0;
 #pragma unroll
             for (int k = 0; k < SPT; ++k) {
-                if (!ok[k]) sm.listed[i & 3][warp][base + __popc(bad[k] & lt_mask)] = (unsigned short)Topo::state(j, k0 + k);
+                if (!ok[k]) sm.listed[i & 1][warp][base + __popc(bad[k] & lt_mask)] = (unsigned short)Topo::state(j, k0 + k);
                 base += __popc(bad[k]);
             }
         }
-        if (lane == 0) sm.n_listed[i & 3][warp] = total;
-        thread_store<Topo, SPT>(nxt, out_chunk + (size_t)Topo::out_row(i, T) * NS, j, k0, res, !POST);
-    };
-
-    // The walk.  `checked` is the last timestep whose verdict has been looked at: rows up to
-    // checked + 1 are final.  After the last timestep the walk goes on for two rounds without
-    // computing, to look at the last two verdicts (either of which can still send it back).
-    int i = 0, checked = -1;
-    unsigned handed = 0u;  // bit k: a list is with checker k and its verdict has not been looked at
-    while (i < T + 2) {
-        if (i < T) {
-            if (scans) scan_step(i);
-            if (POST && !scans && next_row <= checked + 1) {
-                pr.emit(sm.alpha[next_row & 3], out_chunk + (size_t)next_row * NS, m0, lane);
-                ++next_row;  // (at most T here, for row T's verdict comes after the last timestep)
-                pr.fetch(bwd_chunk + (size_t)next_row * NS, lane);
-            }
-            if (copies && i + 1 < T) landed(i + 1);  // the barrier hands the news to everybody
-            ofd::named_bar_sync<kBarStep, kWalkers>();
-        }
-        const int d = i - 2;
-        if (d > checked) {
-            const int k = d & 1;
-            ofd::named_bar_sync2<kBarDone, kWalkers + 32>(k);
-            handed &= ~(1u << k);
-            const int nw = *(volatile int *)&sm.n_wrong[k];
-            checked = d;
-            if (copies && d + RING < T) fill(d + RING);  // nobody reads score row d any more
-            if (nw) {
-                // Row d+1 had wrong guesses; the checker has put the right values there.  What
-                // the other checker is doing rests on that row or on its consequences: wait for
-                // it to finish and ignore what it says.  Then once more from timestep d+1.
-                if (handed) {  // (bit k is clear)
-                    ofd::named_bar_sync2<kBarDone, kWalkers + 32>(k ^ 1);
-                    handed = 0u;
-                }
-                i = d + 1;
-                if (scans) {
+        if (lane == 0) sm.n_listed[i & 1][warp] = total;
+        thread_store<Topo, SPT>(nxt, gmem_out, j, k0, res, !POST);
+        __syncthreads();
+        if (sm.n_wrong[i & 1]) {
+            __syncthreads();  // the checker is correcting this row's readers
 #pragma unroll
-                    for (int q = 0; q < SPT; ++q) res[q] = sm.alpha[i & 3][Topo::state(j, k0 + q)];
-                }
-                continue;
-            }
+            for (int k = 0; k < SPT; ++k) res[k] = nxt[Topo::state(j, k0 + k)];  // maybe corrected
         }
-        if (i < T) {
-            if (tid == 0) sm.work_step[i & 1] = i;
-            __threadfence_block();
-            ofd::named_bar_arrive2<kBarWork, kWalkers + 32>(i & 1);
-            handed |= 1u << (i & 1);
-        }
-        ++i;
+        float *const was_in = const_cast<float *>(in);
+        in = nxt;
+        nxt = spare;
+        spare = was_in;
+        row = (row == sm.ring[RING - 1]) ? sm.ring[0] : row + Smem::kRowBytes;
+        gmem_out += gmem_step;
     }
-    // no more work for the checkers
-    if (tid == 0) sm.work_step[0] = sm.work_step[1] = -1;
-    __threadfence_block();
-    ofd::named_bar_arrive<kBarWork, kWalkers + 32>();
-    ofd::named_bar_arrive<kBarWork + 1, kWalkers + 32>();
-    if (POST && !scans) {
-        while (next_row <= T) {  // every row is final now
-            pr.emit(sm.alpha[next_row & 3], out_chunk + (size_t)next_row * NS, m0, lane);
-            ++next_row;
-            if (next_row <= T) pr.fetch(bwd_chunk + (size_t)next_row * NS, lane);
-        }
-    }
-    if (copies && sm.abort_flag) ofd::mbar_drain_bounded(sm.full, RING, issued, wait_ns);
+    if (POST) __syncthreads();  // the last row is final
 }
 
 // ------------------------------------------------------------------------------------------
@@ -728,8 +737,8 @@ cudaError_t of_launch_forward_posterior(const void *scores_fp16, const float *bw
     const __half *s = static_cast<const __half *>(scores_fp16);
     if (T < 1) return cudaErrorInvalidValue;
     switch (state_len) {
-        case 4: return launch_spec_posterior<256, 4, 8>(s, bwd, post, T, N, stay, tables, status, wait_ns, stream);
-        case 5: return launch_spec_posterior<1024, 4, 8>(s, bwd, post, T, N, stay, tables, status, wait_ns, stream);
+        case 4: return launch_spec_posterior<256, 4, 6>(s, bwd, post, T, N, stay, tables, status, wait_ns, stream);
+        case 5: return launch_spec_posterior<1024, 4, 6>(s, bwd, post, T, N, stay, tables, status, wait_ns, stream);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -740,8 +749,8 @@ cudaError_t of_launch_scans(const void *scores_fp16, float *bwd, float *fwd, int
     const __half *s = static_cast<const __half *>(scores_fp16);
     switch (state_len) {
         case 3: return launch<64, 1, 2, 8>(s, bwd, fwd, T, N, stay, tables, status, wait_ns, stream);
-        case 4: return launch_spec<256, 4, 8>(s, bwd, fwd, T, N, stay, tables, status, wait_ns, stream);
-        case 5: return launch_spec<1024, 4, 8>(s, bwd, fwd, T, N, stay, tables, status, wait_ns, stream);
+        case 4: return launch_spec<256, 4, 6>(s, bwd, fwd, T, N, stay, tables, status, wait_ns, stream);
+        case 5: return launch_spec<1024, 4, 6>(s, bwd, fwd, T, N, stay, tables, status, wait_ns, stream);
         default: return cudaErrorInvalidValue;
     }
 }

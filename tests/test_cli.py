@@ -62,3 +62,17 @@ def test_tensor_dump_matches_the_fixture(cli, tmp_path, oracle_mod):
     assert np.abs(q - ref["qstring"].astype(int)).max() <= 1
     for name, per in (("qual_data", 4), ("base_probs", 1), ("total_probs", 1)):
         assert os.path.getsize(tmp_path / (name + ".blob")) == N * T * per * 4
+    # the reference's way of looking at such dumps (test/compare_blob.cpp:49-73): largest and mean
+    # absolute difference and number of differing elements against stored tensors
+    cmp_bin = os.path.join(os.path.dirname(cli), "compare_blob")
+    for name, key, worst in (("bwd_NTC", "bwd", 0.0), ("post_NTC", "post", 1e-3), ("qual_data", "qual", 1e-3),
+                             ("total_probs", "total_probs", 1e-3)):
+        # (the fixture was decoded with DECODER_INIT; none of these tensors depends on q_scale/q_shift)
+        g[key].astype(np.float32).tofile(tmp_path / "want.blob")
+        r = subprocess.run([cmp_bin, name + ".blob", "want.blob"], capture_output=True, text=True, cwd=tmp_path)
+        assert r.returncode == 0, r.stderr
+        max_diff, avg_diff, tens_len, n_diffs = r.stdout.split()
+        assert int(tens_len) == g[key].size and "tensor max elem diff by" in r.stderr
+        assert float(max_diff) <= worst and float(avg_diff) <= worst, (name, r.stdout)
+        if name == "bwd_NTC":
+            assert int(n_diffs) == 0

@@ -367,6 +367,22 @@ def test_full_size_sup_and_fast_parity(native_lib, oracle_mod, sl, N, seed, piec
     assert identical == N  # every chunk has been identical so far; the gate itself is 99.9 %
 
 
+def test_a_shard_decoded_alone_equals_the_same_chunks_inside_a_larger_batch(native_lib):
+    # chunks 8..11 of a job, generated and decoded on their own (what one GPU of several does),
+    # against the same chunks decoded as part of the whole 16-chunk batch
+    import torch
+    from openfish_b200 import synth
+    of = native_lib
+    sl, T = 4, 700
+    whole = synth.make_scores_device(T, 16, sl, 0x0F16, "cuda")
+    part = synth.make_scores_device(T, 4, sl, 0x0F16, "cuda", first_chunk=8)
+    assert torch.equal(part, whole[:, 8:12])
+    a = gpu_decode(of, whole.cpu().numpy(), sl)
+    b = gpu_decode(of, part.cpu().numpy(), sl)
+    for k in b:
+        assert np.array_equal(a[k][8:12], b[k]), k
+
+
 def test_hardware_approximations_are_within_the_certificates_bounds(native_lib):
     # the certified fp32 log-sum-exp assumes error bounds of ex2.approx and lg2.approx; the library
     # measures both over their whole domains on this GPU
