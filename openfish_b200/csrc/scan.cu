@@ -502,7 +502,7 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
                     }
                     float v[5];
                     terms_of<Topo>(s, sm.alpha[(i - 1) % 3], sm.ring[(i - 1) % RING], stay, v);
-                    const float x = ofx::lse5_exact(v, tr);
+                    const float x = ofx::lse5_exact(v, tr, e < total);
                     const bool wrong = e < total && __float_as_uint(x) != __float_as_uint(sm.alpha[i % 3][s]);
                     const uint32_t wm = __ballot_sync(0xffffffffu, wrong);
                     if (wrong) {
@@ -543,7 +543,7 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
                     float v[5];
                     terms_of<Topo>(dep, sm.alpha[i % 3], sm.ring[i % RING], stay, v);
                     float x;  // certified fp32 evaluation first: it settles all but about 1 in 100
-                    if (!ofd::lse5_try_fast(v, x)) x = ofx::lse5_exact(v, tr);
+                    if (!ofd::lse5_try_fast(v, x)) x = ofx::lse5_exact(v, tr, idx < 5 * nw);
                     sm.alpha[(i + 1) % 3][dep] = x;
                     if (!POST) this_row[dep] = x;
                 }
@@ -611,7 +611,7 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
                 const int st = sm.redo_state[warp][e < total ? e : 0];
                 float w[5];
                 terms_of<Topo>(st, in, row, stay, w);
-                const float x = ofx::lse5_exact(w, tr);
+                const float x = ofx::lse5_exact(w, tr, e < total);
                 if (e < total) sm.redo_value[warp][e] = x;
             }
             __syncwarp();

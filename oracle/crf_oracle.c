@@ -61,6 +61,11 @@ static float lse5(const float v[5]) {
     return top + log(acc);
 }
 
+/* exported for the arithmetic checks of the CUDA path's log-sum-exp: n evaluations, v[5n] */
+void oracle_lse5_many(const float *v, int n, float *out) {
+    for (int i = 0; i < n; ++i) out[i] = lse5(v + 5 * i);
+}
+
 /* Backward scores of one chunk.  src/decode_cpu.c:13-52.  Row T is zero; row t is built from
  * row t+1.  State s can stay (fixed score 2.0f, :14) or move to u = (4s mod ns) + b; that
  * transition's score sits at column 4u + (4s div ns) of timestep t (:33-35,41-42).

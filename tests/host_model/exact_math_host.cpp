@@ -46,3 +46,31 @@ extern "C" float host_fold2(float x, float y) { return ofx::fold2_exact(x, y, of
 extern "C" double host_exp_neg(double a) { return ofx::exp_neg(a, tables()->exp2_j); }
 extern "C" double host_log_1to8(double y) { return ofx::log_1to8(y, tables()->rcp_c, tables()->log_c); }
 extern "C" double host_round_to_f32(double y) { return ofx::round_to_f32(y); }
+
+// single evaluations: the two-tier routine, its tiers on their own, the confirmation shortcut
+extern "C" float host_lse5(const float *v) { return ofx::lse5_exact(v, ofx::ref_of(tables())); }
+extern "C" float host_lse5_tier1(const float *v, int *near) {
+    bool n = false;
+    const float r = ofx::lse5_tier1(v, ofx::ref_of(tables()), n);
+    *near = n;
+    return r;
+}
+extern "C" float host_lse5_tier2(const float *v) { return ofx::lse5_tier2(v[0], v[1], v[2], v[3], v[4], ofx::ref_of(tables())); }
+extern "C" int host_lse5_confirm(const float *v, float guess) { return ofx::lse5_confirm(v, guess, ofx::ref_of(tables())); }
+extern "C" double host_exp_of(double x) { return ofx::exp_of(x, tables()->exp2_j); }
+extern "C" double host_exp_of_t2(double x) { return ofx::exp_of_t2(x, tables()->exp2_j); }
+extern "C" double host_log_1to8_t2(double y) { return ofx::log_1to8_t2(y, tables()->rcp_c, tables()->log_c); }
+// many evaluations at once: out[i] = two-tier result, flags[i] = first tier asked for the second,
+// confirmed[i] = the shortcut confirmed guess[i]
+extern "C" void host_lse5_many(const float *v, const float *guess, int n, float *out, unsigned char *flags,
+                               unsigned char *confirmed) {
+    const ofx::TabRef tr = ofx::ref_of(tables());
+    for (int i = 0; i < n; ++i) {
+        bool near = false;
+        const float r1 = ofx::lse5_tier1(v + 5 * i, tr, near);
+        const float *w = v + 5 * i;
+        out[i] = near ? ofx::lse5_tier2(w[0], w[1], w[2], w[3], w[4], tr) : r1;
+        flags[i] = near;
+        confirmed[i] = ofx::lse5_confirm(v + 5 * i, guess[i], tr);
+    }
+}
