@@ -79,6 +79,24 @@ void openfish_b200_decode_submit_on(void *cuda_stream, int T, int N, int C, cons
  * in the host buffers still need openfish_b200_decode_wait. */
 void openfish_b200_stream_wait_decode(void *cuda_stream, const openfish_gpubuf_t *gpubuf);
 
+/* Submit for scores that carry the blank column: [T][N][5*4^state_len] fp16, five consecutive
+ * entries per state, its stay ("blank") score first and then its four transition scores in the
+ * order of the 4-wide layout (the layout of bonito-style CRF heads).  The reference has no such
+ * entry point -- its driver only ever builds 4*4^state_len columns (reference src/main.c:221) and
+ * its decoders take the stay score from options->blank_score -- so what this call does is this
+ * library's own definition: every state's first entry is dropped, the other four are clamped to
+ * [-clamp, +clamp] when clamp > 0 (such heads bound their scores, usually at 5; 0 = no clamp),
+ * the result goes into a 4-wide copy that the gpubuf allocates on the first such call
+ * (T*N*4*4^state_len*2 bytes, released with the gpubuf), and that copy is decoded exactly as by
+ * openfish_b200_decode_submit, stay score = options->blank_score.  The extra pass is bound by HBM
+ * (it reads 1.25 and writes 1 times the size of the 4-wide tensor).  cuda_stream: the stream the
+ * scores were produced on, as in openfish_b200_decode_submit_on, or NULL for the legacy default
+ * stream.  scores_TN5 must be 16-byte aligned.  Finish with openfish_b200_decode_wait. */
+void openfish_b200_decode_submit_5wide(void *cuda_stream, int T, int N, const void *scores_TN5, int state_len,
+                                       const openfish_opt_t *options, float clamp,
+                                       const openfish_gpubuf_t *gpubuf, uint8_t *moves, char *sequence,
+                                       char *qstring);
+
 /* Device time, in milliseconds, of the gpubuf's last completed decode, measured with CUDA
  * events on the streams the kernels ran on: ms[0] backward scan kernel, ms[1] everything between
  * it and the copies (the beam search kernel with the forward scan kernel beside it on a second

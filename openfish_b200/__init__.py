@@ -76,6 +76,9 @@ def lib():
             getattr(L, name).argtypes = dec + [vp] * 3
         L.openfish_b200_decode_submit_on.restype = None
         L.openfish_b200_decode_submit_on.argtypes = [vp] + dec + [vp] * 3
+        L.openfish_b200_decode_submit_5wide.restype = None
+        L.openfish_b200_decode_submit_5wide.argtypes = [vp, i, i, vp, i, C.POINTER(Opt), C.c_float,
+                                                        C.POINTER(GpuBufStruct)] + [vp] * 3
         L.openfish_b200_stream_wait_decode.restype = None
         L.openfish_b200_stream_wait_decode.argtypes = [vp, C.POINTER(GpuBufStruct)]
         L.openfish_b200_selfcheck_wait.restype = i
@@ -207,6 +210,24 @@ def decode_into(scores_TNC, state_len, gpubuf, moves, sequence, qstring, options
         fn = lib().openfish_b200_decode_into if wait else lib().openfish_b200_decode_submit
         fn(*args, *out)
     _check()
+
+
+def decode_5wide_into(scores_TN5, state_len, gpubuf, moves, sequence, qstring, options=None, clamp=0.0,
+                      stream=None):
+    """openfish_b200_decode_submit_5wide + _wait: scores [T][N][5*4^state_len] (stay score first in
+    every state's five entries), results into caller-owned uint8 host tensors [N][T]."""
+    import torch
+    if not (isinstance(scores_TN5, torch.Tensor) and scores_TN5.is_cuda and scores_TN5.dtype == torch.float16
+            and scores_TN5.is_contiguous() and scores_TN5.dim() == 3
+            and scores_TN5.shape[2] == 5 * 4 ** state_len):
+        raise TypeError("scores_TN5 must be a contiguous CUDA float16 tensor [T][N][5*4^state_len]")
+    T, N, _ = scores_TN5.shape
+    lib().openfish_b200_decode_submit_5wide(stream.cuda_stream if stream is not None else None, T, N,
+                                            scores_TN5.data_ptr(), state_len, C.byref(options or decoder_init()),
+                                            clamp, gpubuf.ptr, moves.data_ptr(), sequence.data_ptr(),
+                                            qstring.data_ptr())
+    _check()
+    decode_wait(gpubuf)
 
 
 def stream_wait_decode(stream, gpubuf):

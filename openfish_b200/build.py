@@ -18,7 +18,7 @@ CLI = os.path.join(HERE, "bin", "openfish")  # the command-line driver, linked a
 CMP_SRC = os.path.join(HERE, "cli", "compare_blob.c")
 CMP = os.path.join(HERE, "bin", "compare_blob")  # tensor-file comparison in the reference's format
 CU = ["scan.cu", "beam_search.cu", "posterior_seq.cu", "rotary.cu", "decode_b200.cu", "decode_static.cu",
-      "selfcheck.cu"]
+      "selfcheck.cu", "adaptor.cu"]
 CC = ["openfish_api.c"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -32,6 +32,12 @@ typedef struct {
 int ofb_decode_submit(int T, int N, int C, const void *scores, int state_len,
                       const ofb_decode_params_t *params, const openfish_gpubuf_t *gpubuf,
                       uint8_t *moves, char *sequence, char *qstring);
+/* The same for scores laid out [T][N][5*4^state_len], every state's stay score in front of its four
+ * transition scores: they are stripped (and clamped to +-clamp when clamp > 0) into a 4-wide copy the
+ * gpubuf owns (allocated on the first such call), which is then decoded. */
+int ofb_decode_submit_5wide(int T, int N, const void *scores5, int state_len, float clamp,
+                            const ofb_decode_params_t *params, const openfish_gpubuf_t *gpubuf,
+                            uint8_t *moves, char *sequence, char *qstring);
 /* Wait for the gpubuf's decode in flight; returns its status (device-side status included). */
 int ofb_decode_wait(const openfish_gpubuf_t *gpubuf);
 int ofb_last_decode_ms(const openfish_gpubuf_t *gpubuf, float ms[8]);

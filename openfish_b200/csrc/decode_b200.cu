@@ -42,6 +42,8 @@ struct GpuBuf {
     float *d_fwd;              // forward scores [N][T+1][ns]: scan kernel -> posterior kernel (64-state model
                                // only; null otherwise: the forward scan kernel writes the posterior)
     int *d_status;
+    void *d_scores4;           // 4-wide copy of 5-wide scores, made on the first 5-wide decode (null before)
+    int sms;
     unsigned char *d_results;  // moves | sequence | qstring, N*T bytes each
     unsigned char *h_stage;    // page-locked, 3*N*T bytes + one status word
     int *h_status;
@@ -100,6 +102,7 @@ int destroy(GpuBuf *g) {
     cudaFree(g->d_tables);
     cudaFree(g->d_fwd);
     cudaFree(g->d_status);
+    cudaFree(g->d_scores4);
     if (g->h_stage) cudaFreeHost(g->h_stage);
     for (int i = 0; i < 8; ++i)
         if (g->ev[i]) cudaEventDestroy(g->ev[i]);
@@ -126,6 +129,7 @@ extern "C" int ofb_gpubuf_create(int T, int N, int state_len, openfish_gpubuf_t 
     const size_t tens = (size_t)N * (T + 1) * ns * sizeof(float);
     int rc = [&]() -> int {
         CU(cudaGetDevice(&g->device));
+        CU(cudaDeviceGetAttribute(&g->sms, cudaDevAttrMultiProcessorCount, g->device));
         // a blocking stream: ordered after work the caller queued on the legacy default
         // stream (where the reference runs), so freshly written scores are seen
         CU(cudaStreamCreateWithFlags(&g->stream, cudaStreamDefault));
@@ -295,6 +299,27 @@ int stream_done_and_status(GpuBuf *g) {
     return OPENFISH_B200_OK;
 }
 }  // namespace
+
+extern "C" int ofb_decode_submit_5wide(int T, int N, const void *scores5, int state_len, float clamp,
+                                       const ofb_decode_params_t *params, const openfish_gpubuf_t *gpubuf,
+                                       uint8_t *moves, char *sequence, char *qstring) {
+    GpuBuf *g = priv(gpubuf);
+    if (g->pending) return fail(OPENFISH_B200_ERR_ARGUMENT, "a decode is already in flight on this gpubuf");
+    int dev = -1;
+    CU(cudaGetDevice(&dev));
+    if (dev != g->device) return fail(OPENFISH_B200_ERR_ARGUMENT, "gpubuf belongs to device %d, current device is %d", g->device, dev);
+    const size_t ns = (size_t)1 << (2 * state_len);
+    if (!g->d_scores4) CU(cudaMalloc(&g->d_scores4, (size_t)T * N * 4 * ns * sizeof(__half)));
+    if (params->on_caller_stream) {
+        cudaStream_t caller = static_cast<cudaStream_t>(params->caller_stream);
+        CU(cudaEventRecord(g->ev[7], caller));
+        CU(cudaStreamWaitEvent(g->stream, g->ev[7], 0));
+    }
+    CU(of_launch_strip_blank(scores5, g->d_scores4, (long long)T * N, state_len, clamp, g->sms, g->stream));
+    ofb_decode_params_t p = *params;
+    p.on_caller_stream = 0;  // (already ordered: the copy above runs on the gpubuf's stream)
+    return ofb_decode_submit(T, N, (int)(4 * ns), g->d_scores4, state_len, &p, gpubuf, moves, sequence, qstring);
+}
 
 extern "C" int ofb_decode_wait(const openfish_gpubuf_t *gpubuf) {
     GpuBuf *g = priv(gpubuf);

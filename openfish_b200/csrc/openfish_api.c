@@ -143,6 +143,31 @@ void openfish_b200_decode_submit_on(void *cuda_stream, int T, int N, int C, cons
     submit(__func__, 1, cuda_stream, T, N, C, scores_TNC, state_len, options, gpubuf, moves, sequence, qstring);
 }
 
+void openfish_b200_decode_submit_5wide(void *cuda_stream, int T, int N, const void *scores_TN5, int state_len,
+                                       const openfish_opt_t *options, float clamp,
+                                       const openfish_gpubuf_t *gpubuf, uint8_t *moves, char *sequence,
+                                       char *qstring) {
+    clear_error();
+    if (!moves || !sequence || !qstring) {
+        raise_error(__func__, OPENFISH_B200_ERR_ARGUMENT, "result buffers must not be NULL");
+        return;
+    }
+    /* same checks as the 4-wide calls, on the 4-wide shape the scores are stripped to */
+    if (state_len < 3 || state_len > 5) {
+        raise_error(__func__, OPENFISH_B200_ERR_ARGUMENT, "state_len not supported (3, 4 or 5)");
+        return;
+    }
+    if (check_decode_args(__func__, T, N, 4 * states_of(state_len), scores_TN5, state_len, options, gpubuf)) return;
+    if (!(clamp >= 0.0f)) {
+        raise_error(__func__, OPENFISH_B200_ERR_ARGUMENT, "clamp must be zero (off) or positive");
+        return;
+    }
+    const ofb_decode_params_t params = {options->beam_cut, options->blank_score, options->q_shift,
+                                        options->q_scale, options->temperature, cuda_stream != NULL, cuda_stream};
+    backend_failed(__func__, ofb_decode_submit_5wide(T, N, scores_TN5, state_len, clamp, &params, gpubuf, moves,
+                                                     sequence, qstring));
+}
+
 void openfish_b200_stream_wait_decode(void *cuda_stream, const openfish_gpubuf_t *gpubuf) {
     clear_error();
     if (!gpubuf) {

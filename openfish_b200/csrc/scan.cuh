@@ -16,6 +16,11 @@ cudaError_t of_launch_scans(const void *scores_fp16, float *bwd, float *fwd, int
 // scores themselves never leave the chip.
 bool of_forward_posterior_fused(int state_len);
 
+// Scores with every state's stay score in front of its four transition scores, [rows][5*ns] fp16,
+// to the [rows][4*ns] layout the decode reads (adaptor.cu); clamp > 0 also bounds the values.
+cudaError_t of_launch_strip_blank(const void *in, void *out, long long rows, int state_len, float clamp, int sms,
+                                  cudaStream_t stream);
+
 // One block, one bounded wait of wait_ns nanoseconds on a barrier that nothing completes (no copy is
 // issued at all); the wait runs out, *status becomes ofd::kStatusWaitTimeout and the kernel returns.
 // Exists so that the path from a kernel's timeout to the host's error can be exercised without anything

@@ -367,6 +367,41 @@ def test_full_size_sup_and_fast_parity(native_lib, oracle_mod, sl, N, seed, piec
     assert identical == N  # every chunk has been identical so far; the gate itself is 99.9 %
 
 
+@pytest.mark.parametrize("sl,T,N,clamp", [(3, 300, 5, 0.0), (4, 200, 3, 5.0), (5, 60, 1, 0.0), (3, 1, 1, 5.0),
+                                          (4, 33, 7, 4.0)])
+def test_scores_with_the_blank_column_inside(native_lib, oracle_mod, sl, T, N, clamp):
+    """The 5-wide entry point.  ADAPTOR PARITY UNPINNED: the reference has no implementation of this
+    layout; the expectation is this library's own definition of it (drop every state's first entry,
+    clamp the other four) written in numpy, followed by the pinned oracle decode."""
+    import torch
+    from openfish_b200 import synth
+    of = native_lib
+    ns = 4 ** sl
+    s4 = synth.make_scores(T, N, sl, 170 + T)           # what the decode should end up seeing (before the clamp)
+    rng = np.random.default_rng(T + N)
+    s5 = np.empty((T, N, ns, 5), np.float16)
+    s5[..., 0] = rng.standard_normal((T, N, ns)).astype(np.float16) * 3   # blank column: must be ignored
+    s5[..., 1:] = s4.reshape(T, N, ns, 4)
+    want4 = np.clip(s4.astype(np.float32), -clamp, clamp) if clamp > 0 else s4.astype(np.float32)
+    ref = oracle_mod.decode(want4, sl, nthreads=4, tensors=True)
+    gb = of.gpubuf_init(T, N, sl)
+    out = [torch.zeros((N, T), dtype=torch.uint8).pin_memory() for _ in range(3)]
+    d5 = torch.from_numpy(s5.reshape(T, N, 5 * ns)).cuda()
+    of.decode_5wide_into(d5, sl, gb, *out, clamp=clamp)
+    got = {k: o.numpy() for k, o in zip(("moves", "sequence", "qstring"), out)}
+    got.update(bwd=gb.tensor("bwd_NTC").cpu().numpy(), post=gb.tensor("post_NTC").cpu().numpy())
+    assert_parity(compare(got, ref), min_identical=1.0)
+    # and once more on a side stream, the scores written there just before the call
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        late = torch.zeros_like(d5)
+        late.copy_(d5)
+        of.decode_5wide_into(late, sl, gb, *out, clamp=clamp, stream=side)
+    for k, o in zip(("moves", "sequence", "qstring"), out):
+        assert np.array_equal(o.numpy(), got[k]), k
+    gb.free()
+
+
 def test_a_shard_decoded_alone_equals_the_same_chunks_inside_a_larger_batch(native_lib):
     # chunks 8..11 of a job, generated and decoded on their own (what one GPU of several does),
     # against the same chunks decoded as part of the whole 16-chunk batch
