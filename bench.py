@@ -321,6 +321,9 @@ def main():
     ap.add_argument("--profile", type=int, metavar="CHUNKS", default=0,
                     help="for captures under a profiler: decode CHUNKS chunks --warmup + --steps times, nothing else")
     ap.add_argument("--profile-model", type=int, default=STATE_LEN, help="state_len of the --profile decode (3, 4 or 5)")
+    ap.add_argument("--profile-timesteps", type=int, default=T, help="T of the --profile decode")
+    ap.add_argument("--profile-rotary", action="store_true",
+                    help="for captures under a profiler: the rotary measurement alone (24 calls on the encoder's QKV shape)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -343,12 +346,16 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
+    if args.profile_rotary:
+        print(json.dumps({"rotary": measure_rotary(of, dev)}), flush=True)
+        return
     if args.profile:
         # the same decode call on a smaller batch, so that a profiler's capture stays small
         sl = args.profile_model
-        sc = synth.make_scores_device(T, args.profile, sl, SEED, dev)
+        sc = synth.make_scores_device(args.profile_timesteps, args.profile, sl, SEED, dev)
         med, _ = timed_decodes(of, sc, sl, steps=args.steps, warmup=args.warmup)
-        print(json.dumps({"profile_chunks": args.profile, "state_len": sl, "T": T, "ms": med}), flush=True)
+        print(json.dumps({"profile_chunks": args.profile, "state_len": sl, "T": args.profile_timesteps, "ms": med}),
+              flush=True)
         return
 
     # this rank's shard: chunks [rank*512, (rank+1)*512) of the job, generated in its own HBM
