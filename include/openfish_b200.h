@@ -105,7 +105,8 @@ void openfish_b200_decode_submit_5wide(void *cuda_stream, int T, int N, const vo
 void openfish_b200_last_decode_ms(const openfish_gpubuf_t *gpubuf, float ms[4]);
 
 /* The same four numbers followed by: ms[4] beam search kernel, ms[5] forward scan kernel, ms[6]
- * posterior + traceback + sequence kernel, ms[7] unused (0). */
+ * posterior + traceback + sequence kernel, ms[7] the blank-column strip in front of a decode
+ * submitted through openfish_b200_decode_submit_5wide (0 otherwise; not part of ms[3]). */
 void openfish_b200_last_decode_detail_ms(const openfish_gpubuf_t *gpubuf, float ms[8]);
 
 /* Device time, in milliseconds, of the calling thread's last openfish_rotary_emb_gpu call (CUDA

@@ -154,7 +154,7 @@ class GpuBuf:
         ms = (C.c_float * 8)()
         lib().openfish_b200_last_decode_detail_ms(self.ptr, ms)
         return dict(bwd_scan=ms[0], rest=ms[1], d2h=ms[2], total=ms[3], beam_search=ms[4],
-                    fwd_scan=ms[5], posterior_seq=ms[6])
+                    fwd_scan=ms[5], posterior_seq=ms[6], strip_blank=ms[7])
 
 
 def gpubuf_init(T, N, state_len):

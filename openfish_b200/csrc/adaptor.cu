@@ -16,9 +16,10 @@
 
 namespace {
 
-// rows a block of 256 threads takes per pass: as many as make one 16-byte output piece per thread
+// rows a block of 256 threads takes per pass: some 20 KB of input, i.e. five 16-byte loads in flight
+// per thread -- a streaming kernel reaches the memory's bandwidth only with enough bytes under way
 template <int NS>
-struct RowsPerPass { static constexpr int value = NS / 2 >= 256 ? 1 : 256 / (NS / 2); };
+struct RowsPerPass { static constexpr int value = 20480 / (NS * 10); };
 
 template <int NS>
 __global__ void __launch_bounds__(256) strip_blank_kernel(const uint4 *__restrict__ in, uint4 *__restrict__ out,
@@ -29,14 +30,22 @@ __global__ void __launch_bounds__(256) strip_blank_kernel(const uint4 *__restric
     __shared__ uint4 stage[RPB][IN16];
     const __half2 lo2 = __float2half2_rn(-clamp), hi2 = __float2half2_rn(clamp);
     for (long long row0 = (long long)blockIdx.x * RPB; row0 < rows; row0 += (long long)gridDim.x * RPB) {
-        for (int i = threadIdx.x; i < RPB * IN16; i += 256) {
-            const int r = i / IN16, c = i % IN16;
-            if (row0 + r < rows) stage[r][c] = __ldcs(in + (row0 + r) * IN16 + c);  // read once: streaming
+        // the rows of a pass are consecutive in memory: one flat range of 16-byte pieces
+        const long long left = (rows - row0) * IN16;
+        const int pieces = left < RPB * IN16 ? (int)left : RPB * IN16;
+        const uint4 *src = in + row0 * IN16;
+        uint4 *flat = &stage[0][0];
+#pragma unroll
+        for (int k = 0; k < (RPB * IN16 + 255) / 256; ++k) {
+            const int i = threadIdx.x + 256 * k;
+            if (i < pieces) flat[i] = __ldcs(src + i);  // read once: streaming
         }
         __syncthreads();
-        for (int i = threadIdx.x; i < RPB * OUT16; i += 256) {
+#pragma unroll
+        for (int k = 0; k < (RPB * OUT16 + 255) / 256; ++k) {
+            const int i = threadIdx.x + 256 * k;
             const int r = i / OUT16, c = i % OUT16;
-            if (row0 + r >= rows) continue;
+            if (i >= RPB * OUT16 || row0 + r >= rows) continue;
             // output piece c holds states 2c and 2c+1: input halfs 10c+1..10c+4 and 10c+6..10c+9
             const __half *h = reinterpret_cast<const __half *>(&stage[r][0]) + 10 * c;
             __half2 p[4] = {__halves2half2(h[1], h[2]), __halves2half2(h[3], h[4]),

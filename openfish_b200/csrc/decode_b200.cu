@@ -34,8 +34,8 @@ struct GpuBuf {
     int T, N, state_len, device;
     cudaStream_t stream;   // everything but the forward scan; blocking, see ofb_gpubuf_create
     cudaStream_t stream2;  // the forward scan, ordered against `stream` by events only
-    cudaEvent_t ev[8];     // 0 start, 1 bwd scan done, 2 beam search done, 3 sequence done, 4 copies done,
-                           // 5 fwd scan start, 6 fwd scan done, 7 the caller's stream at submit time
+    cudaEvent_t ev[9];     // 0 start, 1 bwd scan done, 2 beam search done, 3 sequence done, 4 copies done,
+                           // 5 fwd scan start, 6 fwd scan done, 7 the caller's stream at submit time, 8 blank-column strip start
     uint64_t wait_ns;      // how long a kernel waits for an asynchronous copy before it raises d_status
     int *d_init_kmers;     // inside the beam_vector allocation, behind the back-pointers
     ofx::Tables *d_tables;
@@ -53,6 +53,7 @@ struct GpuBuf {
     char *dst_sequence, *dst_qstring;
     bool via_stage;
     float ms[8];
+    bool stripped = false;  // the decode in flight began with the blank-column strip
 };
 
 thread_local char g_err[512] = "";
@@ -104,7 +105,7 @@ int destroy(GpuBuf *g) {
     cudaFree(g->d_status);
     cudaFree(g->d_scores4);
     if (g->h_stage) cudaFreeHost(g->h_stage);
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < 9; ++i)
         if (g->ev[i]) cudaEventDestroy(g->ev[i]);
     if (g->stream2) cudaStreamDestroy(g->stream2);
     if (g->stream) cudaStreamDestroy(g->stream);
@@ -134,7 +135,7 @@ extern "C" int ofb_gpubuf_create(int T, int N, int state_len, openfish_gpubuf_t 
         // stream (where the reference runs), so freshly written scores are seen
         CU(cudaStreamCreateWithFlags(&g->stream, cudaStreamDefault));
         CU(cudaStreamCreateWithFlags(&g->stream2, cudaStreamNonBlocking));
-        for (int i = 0; i < 8; ++i) CU(cudaEventCreate(&g->ev[i]));
+        for (int i = 0; i < 9; ++i) CU(cudaEventCreate(&g->ev[i]));
         g->wait_ns = ofd::kDefaultWaitLimitNs;
         // same ten buffers and sizes as the reference (src/decode_cuda.cu:22-45); the three
         // result arrays share one allocation so that one copy brings them back
@@ -315,7 +316,9 @@ extern "C" int ofb_decode_submit_5wide(int T, int N, const void *scores5, int st
         CU(cudaEventRecord(g->ev[7], caller));
         CU(cudaStreamWaitEvent(g->stream, g->ev[7], 0));
     }
+    CU(cudaEventRecord(g->ev[8], g->stream));
     CU(of_launch_strip_blank(scores5, g->d_scores4, (long long)T * N, state_len, clamp, g->sms, g->stream));
+    g->stripped = true;
     ofb_decode_params_t p = *params;
     p.on_caller_stream = 0;  // (already ordered: the copy above runs on the gpubuf's stream)
     return ofb_decode_submit(T, N, (int)(4 * ns), g->d_scores4, state_len, &p, gpubuf, moves, sequence, qstring);
@@ -335,7 +338,8 @@ extern "C" int ofb_decode_wait(const openfish_gpubuf_t *gpubuf) {
     }
     // ms: 0 backward scan, 1 everything between it and the copies (beam search with the forward
     // scan beside it, then posterior + sequence), 2 copies, 3 all of it; detail: 4 beam search,
-    // 5 forward scan, 6 posterior + sequence (from the later of its two inputs), 7 unused
+    // 5 forward scan, 6 posterior + sequence (from the later of its two inputs), 7 the blank-column
+    // strip in front of a 5-wide decode (0 otherwise)
     cudaEventElapsedTime(&g->ms[0], g->ev[0], g->ev[1]);
     cudaEventElapsedTime(&g->ms[1], g->ev[1], g->ev[3]);
     cudaEventElapsedTime(&g->ms[2], g->ev[3], g->ev[4]);
@@ -347,6 +351,8 @@ extern "C" int ofb_decode_wait(const openfish_gpubuf_t *gpubuf) {
     cudaEventElapsedTime(&from_fwd, g->ev[6], g->ev[3]);
     g->ms[6] = from_beam < from_fwd ? from_beam : from_fwd;
     g->ms[7] = 0.f;
+    if (g->stripped) cudaEventElapsedTime(&g->ms[7], g->ev[8], g->ev[0]);
+    g->stripped = false;
     return OPENFISH_B200_OK;
 }
 
