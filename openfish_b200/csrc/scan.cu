@@ -361,7 +361,10 @@ struct SpecSmem {
     double rcp_c[ofx::kLogTab];
     double log_c[ofx::kLogTab];
     alignas(8) uint64_t full[RING];
-    unsigned short listed[2][NW][kPerWarp];
+    // A listed state is handed to the checker with all it needs: its five terms, the guess and
+    // the state's number (32 bytes), so that the checker's chain starts with one round trip to
+    // shared memory instead of three dependent ones (list, then state, then the state's inputs).
+    alignas(16) float4 listed[2][NW][kPerWarp][2];  // {v0 v1 v2 v3} {v4 guess state -}
     int n_listed[2][NW];
     int n_wrong[2];
     unsigned short wrong_state[NW * kPerWarp];
@@ -483,34 +486,72 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
         __syncthreads();  // start of the scan
         for (int i = 0; i <= T; ++i) {
             // During timestep i (for i = T: after the last one) check the states listed during
-            // timestep i-1: inputs alpha[(i-1)%3], scores in slot (i-1)%RING, guesses in
+            // timestep i-1; their terms and guesses come with the list, the guesses also stand in
             // alpha[i%3] and in the output row of timestep i-1.
             int nw = 0;
             if (i >= 1) {
                 const int par = (i - 1) & 1;
-                int total = 0;
+                // An entry was written before the correction that ended its timestep, if there
+                // was one: a state that read a corrected value stands on the list with the terms
+                // from before.  The correction has recomputed every such state for good, so a
+                // mismatch counts only if the entry's terms are still the state's terms.
+                auto still_stands = [&](bool differs, const float (&v)[5], int s) {
+                    if (__any_sync(0xffffffffu, differs)) {  // one timestep in seventeen
+                        float now[5];
+                        terms_of<Topo>(differs ? s : 0, sm.alpha[(i - 1) % 3], sm.ring[(i - 1) % RING], stay, now);
 #pragma unroll
-                for (int w = 0; w < NW; ++w) total += sm.n_listed[par][w];
-                for (int base = 0; base < total; base += 32) {
-                    const int e = base + lane;
-                    int s = 0, acc = 0;
+                        for (int q = 0; q < 5; ++q) differs = differs && __float_as_uint(now[q]) == __float_as_uint(v[q]);
+                    }
+                    return differs;
+                };
+                if (NW * PER <= 32) {
+                    // a lane per slot: nothing to look up before the entry can be fetched
+                    const int w = lane / PER, k = lane % PER;
+                    const float4 a = sm.listed[par][w < NW ? w : 0][k][0], b = sm.listed[par][w < NW ? w : 0][k][1];
+                    const bool mine = w < NW && k < sm.n_listed[par][w < NW ? w : 0];
+                    if (__any_sync(0xffffffffu, mine)) {
+                        const float v[5] = {a.x, a.y, a.z, a.w, b.x};
+                        const float x = ofx::lse5_exact(v, tr, mine);
+                        const bool wrong = still_stands(mine && __float_as_uint(x) != __float_as_uint(b.y), v, __float_as_int(b.z));
+                        const uint32_t wm = __ballot_sync(0xffffffffu, wrong);
+                        if (wrong) {
+                            const int at = __popc(wm & ((1u << lane) - 1u));
+                            sm.wrong_state[at] = (unsigned short)__float_as_int(b.z);
+                            sm.wrong_value[at] = x;
+                        }
+                        nw = __popc(wm);
+                    }
+                } else {
+                    // more slots than lanes: the filled ones are taken 32 at a time
+                    int cnt[NW], total = 0;
 #pragma unroll
                     for (int w = 0; w < NW; ++w) {
-                        const int c = sm.n_listed[par][w];
-                        if (e >= acc && e < acc + c) s = sm.listed[par][w][e - acc];
-                        acc += c;
+                        cnt[w] = sm.n_listed[par][w];
+                        total += cnt[w];
                     }
-                    float v[5];
-                    terms_of<Topo>(s, sm.alpha[(i - 1) % 3], sm.ring[(i - 1) % RING], stay, v);
-                    const float x = ofx::lse5_exact(v, tr, e < total);
-                    const bool wrong = e < total && __float_as_uint(x) != __float_as_uint(sm.alpha[i % 3][s]);
-                    const uint32_t wm = __ballot_sync(0xffffffffu, wrong);
-                    if (wrong) {
-                        const int at = nw + __popc(wm & ((1u << lane) - 1u));
-                        sm.wrong_state[at] = (unsigned short)s;
-                        sm.wrong_value[at] = x;
+                    for (int base = 0; base < total; base += 32) {
+                        const int e = base + lane;
+                        int at_w = 0, at_k = 0, acc = 0;
+#pragma unroll
+                        for (int w = 0; w < NW; ++w) {
+                            if (e >= acc && e < acc + cnt[w]) {
+                                at_w = w;
+                                at_k = e - acc;
+                            }
+                            acc += cnt[w];
+                        }
+                        const float4 a = sm.listed[par][at_w][at_k][0], b = sm.listed[par][at_w][at_k][1];
+                        const float v[5] = {a.x, a.y, a.z, a.w, b.x};
+                        const float x = ofx::lse5_exact(v, tr, e < total);
+                        const bool wrong = still_stands(e < total && __float_as_uint(x) != __float_as_uint(b.y), v, __float_as_int(b.z));
+                        const uint32_t wm = __ballot_sync(0xffffffffu, wrong);
+                        if (wrong) {
+                            const int at = nw + __popc(wm & ((1u << lane) - 1u));
+                            sm.wrong_state[at] = (unsigned short)__float_as_int(b.z);
+                            sm.wrong_value[at] = x;
+                        }
+                        nw += __popc(wm);
                     }
-                    nw += __popc(wm);
                 }
                 __syncwarp();
             }
@@ -623,7 +664,11 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
             int base = 0;
 #pragma unroll
             for (int k = 0; k < SPT; ++k) {
-                if (!ok[k]) sm.listed[i & 1][warp][base + __popc(bad[k] & lt_mask)] = (unsigned short)Topo::state(j, k0 + k);
+                if (!ok[k]) {
+                    float4 *entry = sm.listed[i & 1][warp][base + __popc(bad[k] & lt_mask)];
+                    entry[0] = make_float4(v[k][0], v[k][1], v[k][2], v[k][3]);
+                    entry[1] = make_float4(v[k][4], res[k], __int_as_float(Topo::state(j, k0 + k)), 0.f);
+                }
                 base += __popc(bad[k]);
             }
         }
