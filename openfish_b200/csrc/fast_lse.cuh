@@ -108,77 +108,4 @@ __device__ __forceinline__ void lse5_fast_guess(const float (*v)[5], float *out,
     }
 }
 
-// K log-sum-exps for one thread: fast path first, value-exact fallback for the states whose
-// rounding the fast path cannot certify.  When most of the warp needs the fallback (the first
-// few hundred timesteps, where scores are small and the float grid is fine) the batched
-// routine does all K at once; otherwise the few lanes concerned redo single states.
-template <int K>
-__device__ __forceinline__ void lse5_batch(const float (*v)[5], float *out, const ofx::TabRef t) {
-    bool ok[K];
-    // all K fast evaluations stage by stage, so that their instruction streams interleave
-    {
-        const float kLog2e = 1.4426950408889634f;
-        float m[K], e[K][5], s[K], l[K];
-#pragma unroll
-        for (int k = 0; k < K; ++k)
-            m[k] = max5(v[k]);
-#pragma unroll
-        for (int i = 0; i < 5; ++i)
-#pragma unroll
-            for (int k = 0; k < K; ++k) e[k][i] = (v[k][i] - m[k]) * kLog2e;
-#pragma unroll
-        for (int i = 0; i < 5; ++i)
-#pragma unroll
-            for (int k = 0; k < K; ++k) e[k][i] = ex2_approx(e[k][i]);
-#pragma unroll
-        for (int k = 0; k < K; ++k) s[k] = e[k][0] + e[k][1];
-#pragma unroll
-        for (int i = 2; i < 5; ++i)
-#pragma unroll
-            for (int k = 0; k < K; ++k) s[k] += e[k][i];
-#pragma unroll
-        for (int k = 0; k < K; ++k) {
-            l[k] = ln_1to8(s[k]);
-        }
-#pragma unroll
-        for (int k = 0; k < K; ++k) {
-            const float lo = m[k] + (l[k] - kLseEps);
-            const float hi = m[k] + (l[k] + kLseEps);
-            out[k] = lo;
-            ok[k] = lo == hi;  // (a NaN sum makes both ends NaN: never accepted)
-        }
-    }
-    int nbad = 0;
-#pragma unroll
-    for (int k = 0; k < K; ++k) nbad += !ok[k];
-    const int fails = __reduce_add_sync(0xffffffffu, nbad);
-    if (fails == 0) return;
-    if (fails > 4 * K) {
-        ofx::lse5_batch_exact<K>(v, out, t);
-        return;
-    }
-    // A few lanes need the exact routine for one of their states: every lane that has one
-    // hands in its first uncertified state, so one pass through the routine serves them all.
-    for (;;) {
-        int pick = -1;
-#pragma unroll
-        for (int k = K - 1; k >= 0; --k) pick = ok[k] ? pick : k;
-        if (!__any_sync(0xffffffffu, pick >= 0)) break;
-        float w[5];
-#pragma unroll
-        for (int i = 0; i < 5; ++i) {
-            w[i] = v[0][i];
-#pragma unroll
-            for (int k = 1; k < K; ++k) w[i] = pick == k ? v[k][i] : w[i];
-        }
-        const float r = ofx::lse5_exact(w, t);
-#pragma unroll
-        for (int k = 0; k < K; ++k)
-            if (pick == k) {
-                out[k] = r;
-                ok[k] = true;
-            }
-    }
-}
-
 }  // namespace ofd

@@ -220,126 +220,14 @@ struct PosteriorRow {
 };
 
 // ------------------------------------------------------------------------------------------
-// Plain variant (the 64-state model: two chunks per block, too little work per timestep for the
-// speculative machinery to pay): CPB chunks per block; uncertified states are settled within the
-// timestep.
-
-template <int NS, int CPB, int RING>
-struct ScanSmem {
-    static constexpr int kRowBytes = NS * 4 * 2;        // one chunk's score row (fp16)
-    static constexpr int kSlotBytes = kRowBytes * CPB;  // one timestep of the block
-    alignas(128) unsigned char ring[RING][kSlotBytes];
-    alignas(16) float alpha[2][CPB][NS];
-    alignas(16) double exp2_rep[ofx::kExpTab * kExpCopies];
-    double rcp_c[ofx::kLogTab];
-    double log_c[ofx::kLogTab];
-    alignas(8) uint64_t full[RING];
-    int abort_flag;
-};
-
-template <class Topo, int NS, int SPT, int CPB, int RING>
-__device__ __forceinline__ void scan_body(unsigned char *smem_raw, int block, const __half *scores,
-                                          float *out, int T, int N, float stay,
-                                          const ofx::Tables *tables, int *status, uint64_t wait_ns) {
-    constexpr int NJ = NS / 4;
-    constexpr int TPC = NS / SPT;
-    static_assert(TPC % 32 == 0, "a warp must not straddle two chunks");
-    using Smem = ScanSmem<NS, CPB, RING>;
-    Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
-
-    const int tid = threadIdx.x;
-    const int cl = tid / TPC;
-    const int j = tid % NJ;
-    const int k0 = ((tid % TPC) / NJ) * SPT;
-    const int chunk0 = block * CPB;
-    const int nlive = min(CPB, N - chunk0);
-    const uint32_t slot_bytes = (uint32_t)nlive * Smem::kRowBytes;
-
-    for (int i = tid; i < ofx::kExpTab * kExpCopies; i += blockDim.x)
-        sm.exp2_rep[i] = tables->exp2_j[i / kExpCopies];
-    for (int i = tid; i < ofx::kLogTab; i += blockDim.x) {
-        sm.rcp_c[i] = tables->rcp_c[i];
-        sm.log_c[i] = tables->log_c[i];
-    }
-    for (int i = tid; i < CPB * NS; i += blockDim.x) (&sm.alpha[0][0][0])[i] = 0.f;
-    if (tid == 0) {
-        sm.abort_flag = 0;
-        for (int r = 0; r < RING; ++r) ofd::mbar_init(&sm.full[r], 1);
-        ofd::mbar_fence_init();
-    }
-    __syncthreads();
-
-    // the scans address scores as [T][N][4ns] whatever C is (src/decode_cpu.c:16-18,27,59-62,80)
-    const size_t t_stride = (size_t)N * NS * 4;
-    const __half *blk_scores = scores + (size_t)chunk0 * NS * 4;
-
-    if (tid >= TPC * CPB) {
-        // ------------------------------------------------------------------ copy warp
-        // Keeps the ring full and takes every mbarrier operation off the scan warps: before it
-        // joins the barrier that ends timestep i it has seen row i+1 land, so the barrier hands
-        // that knowledge (and the data) to everybody; after it the slot of row i is refilled.
-        const bool issuer = tid == TPC * CPB;
-        int issued = 0;  // copies go out in row order; after an abort no more are issued
-        if (issuer) {
-            for (int i = 0; i < RING && i < T; ++i, ++issued) {
-                ofd::mbar_arrive_expect_tx(&sm.full[i], slot_bytes);
-                ofd::bulk_g2s(sm.ring[i], blk_scores + t_stride * (size_t)Topo::score_row(i, T), slot_bytes,
-                              &sm.full[i]);
-            }
-            if (T > 0) ofd::mbar_wait_bounded(&sm.full[0], 0u, &sm.abort_flag, status, wait_ns);
-        }
-        __syncthreads();
-        for (int i = 0; i < T; ++i) {
-            if (issuer && i + 1 < T)
-                ofd::mbar_wait_bounded(&sm.full[(i + 1) % RING], (uint32_t)((i + 1) / RING) & 1u,
-                                       &sm.abort_flag, status, wait_ns);
-            __syncthreads();
-            if (issuer && i + RING < T && !sm.abort_flag) {
-                const int slot = i % RING;
-                ofd::mbar_arrive_expect_tx(&sm.full[slot], slot_bytes);
-                ofd::bulk_g2s(sm.ring[slot], blk_scores + t_stride * (size_t)Topo::score_row(i + RING, T),
-                              slot_bytes, &sm.full[slot]);
-                ++issued;
-            }
-        }
-        if (issuer && sm.abort_flag) ofd::mbar_drain_bounded(sm.full, RING, issued, wait_ns);
-        return;
-    }
-
-    const int chunk = chunk0 + cl;
-    const bool live = chunk < N;
-    const ofx::TabRef tr = {sm.exp2_rep + (tid & (kExpCopies - 1)), kExpCopies, sm.rcp_c, sm.log_c};
-    float *out_chunk = out + (size_t)(live ? chunk : 0) * (size_t)(T + 1) * NS;
-    if (live) {
-#pragma unroll
-        for (int k = 0; k < SPT; ++k) out_chunk[(size_t)Topo::zero_row(T) * NS + Topo::state(j, k0 + k)] = 0.f;
-    }
-    __syncthreads();
-
-    for (int i = 0; i < T; ++i) {
-        float res[SPT];
-#pragma unroll
-        for (int k = 0; k < SPT; ++k) res[k] = 0.f;
-        if (live) {  // a padding chunk of the last block has no data to work on
-            float v[SPT][5];
-            thread_terms<Topo, SPT>(sm.alpha[i & 1][cl], sm.ring[i % RING] + cl * Smem::kRowBytes, j, k0, stay, v);
-            ofd::lse5_batch<SPT>(v, res, tr);
-        }
-        thread_store<Topo, SPT>(sm.alpha[(i & 1) ^ 1][cl], out_chunk + (size_t)Topo::out_row(i, T) * NS, j, k0,
-                                res, live);
-        __syncthreads();  // row complete; the copy warp has confirmed the next score row
-    }
-}
-
-// ------------------------------------------------------------------------------------------
-// Speculative variant (one chunk per block; the 256- and 1024-state models).
+// The scan of one chunk by one block.
 //
-// In the plain variant a state whose rounding the fp32 evaluation cannot certify sends its whole
-// warp through the value-exact routine before the timestep can end, and almost every timestep
-// has a few such states: the exact routine's latency is paid on nearly every step.  Here the
-// scan warps do not wait for it.  An uncertified state gets the likelier of its two candidate
-// floats and is put on a list; while the scan warps work on the next timestep, a checker warp
-// recomputes the listed states exactly.  If every guess was right (about three timesteps in
+// If a state whose rounding the fp32 evaluation cannot certify sent its warp through the
+// value-exact routine before the timestep could end, that routine's latency would be paid on
+// nearly every step: almost every timestep has a few such states.  Here the scan warps do not
+// wait for it.  An uncertified state gets the likelier of its two candidate floats and is put on
+// a list, together with its five terms; while the scan warps work on the next timestep, a
+// checker warp recomputes the listed states exactly.  If every guess was right (about three timesteps in
 // four) nothing else happens.  If one was wrong the block pauses at the end of that next
 // timestep: the checker corrects the value and recomputes exactly the five states of the next
 // row that read it (the state itself and its four readers) before anybody reads those, and the
@@ -366,7 +254,6 @@ struct SpecSmem {
     // shared memory instead of three dependent ones (list, then state, then the state's inputs).
     alignas(16) float4 listed[2][NW][kPerWarp][2];  // {v0 v1 v2 v3} {v4 guess state -}
     int n_listed[2][NW];
-    int n_wrong[2];
     unsigned short wrong_state[NW * kPerWarp];
     float wrong_value[NW * kPerWarp];
     // settle-now path: a warp's uncertified states, dealt out to its lanes, and their exact values
@@ -406,7 +293,6 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
     for (int i = tid; i < NS; i += blockDim.x) sm.alpha[0][i] = 0.f;
     if (tid == 0) {
         sm.abort_flag = 0;
-        sm.n_wrong[0] = sm.n_wrong[1] = 0;
         for (int r = 0; r < RING; ++r) ofd::mbar_init(&sm.full[r], 1);
         ofd::mbar_fence_init();
     }
@@ -441,8 +327,7 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
         __syncthreads();
         for (int i = 0; i < T; ++i) {
             if (issuer && i + 1 < T) landed(i + 1);
-            __syncthreads();
-            if (sm.n_wrong[i & 1]) __syncthreads();
+            if (__syncthreads_or(0)) __syncthreads();
             if (issuer && i >= 1 && i - 1 + RING < T) fill(i - 1 + RING);
         }
         if (POST) __syncthreads();  // the last row is final
@@ -468,8 +353,7 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
                 ++next_row;
                 fetch(next_row);  // next_row <= T
             }
-            __syncthreads();
-            if (sm.n_wrong[i & 1]) __syncthreads();
+            if (__syncthreads_or(0)) __syncthreads();
         }
         while (next_row <= T - 1) {  // final since the last timestep's barrier
             emit(next_row);
@@ -566,8 +450,8 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
                 }
                 break;
             }
-            if (lane == 0) sm.n_wrong[i & 1] = nw;
-            __syncthreads();  // end of timestep i
+            // end of timestep i; the barrier itself tells every warp whether a guess was wrong
+            __syncthreads_or(nw);
             if (nw) {
                 float *prev_row = out_chunk + (size_t)Topo::out_row(i - 1, T) * NS;
                 for (int e = lane; e < nw; e += 32) {
@@ -618,18 +502,34 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
         thread_terms<Topo, SPT>(in, row, j, k0, stay, v, res);
         ofd::lse5_fast_guess<SPT>(v, res, ok);
         uint32_t bad[SPT];
-        int total = 0;
-        bool all_ok = true;
+        int total = 0, mine = 0;
 #pragma unroll
-        for (int k = 0; k < SPT; ++k) all_ok = all_ok && ok[k];
-        if (__any_sync(0xffffffffu, !all_ok)) {  // about every other timestep per warp
+        for (int k = 0; k < SPT; ++k) mine += !ok[k];
+        const uint32_t owners = __ballot_sync(0xffffffffu, mine != 0);  // non-zero about every other timestep per warp
+        // The usual case: a few lanes with one uncertified state each.  One vote settles who lists
+        // where; anything else takes the general route below.
+        const bool few = owners != 0 && __popc(owners) <= PER && !__any_sync(0xffffffffu, mine > 1);
+        if (few) {
+            if (mine) {
+                float4 *entry = sm.listed[i & 1][warp][__popc(owners & lt_mask)];
+#pragma unroll
+                for (int k = 0; k < SPT; ++k) {
+                    if (ok[k]) continue;
+                    entry[0] = make_float4(v[k][0], v[k][1], v[k][2], v[k][3]);
+                    entry[1] = make_float4(v[k][4], res[k], __int_as_float(Topo::state(j, k0 + k)), 0.f);
+                }
+            }
+            total = __popc(owners);
+        } else if (owners) {
 #pragma unroll
             for (int k = 0; k < SPT; ++k) {
                 bad[k] = __ballot_sync(0xffffffffu, !ok[k]);
                 total += __popc(bad[k]);
             }
         }
-        if (total > 16 * SPT) {
+        if (few) {
+            // listed above
+        } else if (total > 16 * SPT) {
             // most states uncertified (the first few dozen timesteps, where scores are small and
             // the float grid fine): the exact routine for every state, straight from registers
             ofx::lse5_batch_exact<SPT>(v, res, tr);
@@ -674,8 +574,7 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
         }
         if (lane == 0) sm.n_listed[i & 1][warp] = total;
         thread_store<Topo, SPT>(nxt, gmem_out, j, k0, res, !POST);
-        __syncthreads();
-        if (sm.n_wrong[i & 1]) {
+        if (__syncthreads_or(0)) {
             __syncthreads();  // the checker is correcting this row's readers
 #pragma unroll
             for (int k = 0; k < SPT; ++k) res[k] = nxt[Topo::state(j, k0 + k)];  // maybe corrected
@@ -694,20 +593,8 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
 // One grid for either or both directions: the first n_bwd_blocks blocks scan backwards, the
 // rest forwards.
 
-template <int NS, int SPT, int CPB, int RING>
-__global__ void __launch_bounds__((NS / SPT) * CPB + 32)
-scan_kernel(const __half *__restrict__ scores, float *__restrict__ bwd, float *__restrict__ fwd,
-            int T, int N, int n_bwd_blocks, float stay, const ofx::Tables *__restrict__ tables, int *status, uint64_t wait_ns) {
-    extern __shared__ unsigned char smem_raw[];
-    if ((int)blockIdx.x < n_bwd_blocks)
-        scan_body<BwdTopo<NS>, NS, SPT, CPB, RING>(smem_raw, blockIdx.x, scores, bwd, T, N, stay, tables, status, wait_ns);
-    else
-        scan_body<FwdTopo<NS>, NS, SPT, CPB, RING>(smem_raw, blockIdx.x - n_bwd_blocks, scores, fwd, T, N, stay, tables,
-                                                   status, wait_ns);
-}
-
 template <int NS, int SPT, int RING>
-__global__ void __launch_bounds__(NS / SPT + 64, (NS <= 256 ? 4 : 2))
+__global__ void __launch_bounds__(NS / SPT + 64, (NS <= 64 ? 8 : NS <= 256 ? 4 : 2))
 scan_spec_kernel(const __half *__restrict__ scores, float *__restrict__ bwd, float *__restrict__ fwd,
                  int T, int N, int n_bwd_blocks, float stay, const ofx::Tables *__restrict__ tables,
                  int *status, uint64_t wait_ns) {
@@ -728,21 +615,6 @@ scan_spec_posterior_kernel(const __half *__restrict__ scores, const float *__res
                            const ofx::Tables *__restrict__ tables, int *status, uint64_t wait_ns) {
     extern __shared__ unsigned char smem_raw[];
     spec_body<FwdTopo<NS>, NS, SPT, RING, true>(smem_raw, blockIdx.x, scores, post, bwd, T, N, stay, tables, status, wait_ns);
-}
-
-template <int NS, int SPT, int CPB, int RING>
-cudaError_t launch(const __half *scores, float *bwd, float *fwd, int T, int N, float stay,
-                   const ofx::Tables *tables, int *status, uint64_t wait_ns, cudaStream_t stream) {
-    using Smem = ScanSmem<NS, CPB, RING>;
-    const size_t bytes = sizeof(Smem) + 128;
-    auto kern = scan_kernel<NS, SPT, CPB, RING>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-    if (e != cudaSuccess) return e;
-    const int nblk = (N + CPB - 1) / CPB;
-    const int n_bwd = bwd ? nblk : 0, n_fwd = fwd ? nblk : 0;
-    kern<<<n_bwd + n_fwd, (NS / SPT) * CPB + 32, bytes, stream>>>(scores, bwd, fwd, T, N, n_bwd, stay, tables,
-                                                                 status, wait_ns);
-    return cudaGetLastError();
 }
 
 template <int NS, int SPT, int RING>
@@ -793,7 +665,7 @@ cudaError_t of_launch_scans(const void *scores_fp16, float *bwd, float *fwd, int
                             uint64_t wait_ns, cudaStream_t stream) {
     const __half *s = static_cast<const __half *>(scores_fp16);
     switch (state_len) {
-        case 3: return launch<64, 1, 2, 8>(s, bwd, fwd, T, N, stay, tables, status, wait_ns, stream);
+        case 3: return launch_spec<64, 1, 8>(s, bwd, fwd, T, N, stay, tables, status, wait_ns, stream);
         case 4: return launch_spec<256, 4, 6>(s, bwd, fwd, T, N, stay, tables, status, wait_ns, stream);
         case 5: return launch_spec<1024, 4, 6>(s, bwd, fwd, T, N, stay, tables, status, wait_ns, stream);
         default: return cudaErrorInvalidValue;
