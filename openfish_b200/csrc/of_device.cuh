@@ -103,6 +103,17 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
         : "memory");
 }
 
+// Eight floats {v0 v1 v2 v3} {v4 a b 0} to 32 bytes of shared memory at `addr` (a shared-window
+// address, 16-byte aligned) if `flag`, as two predicated stores: no branch, so no divergence.
+__device__ __forceinline__ void sts_entry_if(bool flag, uint32_t addr, const float (&v)[5], float a, float b) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %0, 0;\n\t"
+        "@p st.shared.v4.f32 [%1], {%2, %3, %4, %5};\n\t"
+        "@p st.shared.v4.f32 [%1+16], {%6, %7, %8, %9};\n\t}"
+        ::"r"((int)flag), "r"(addr), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(a), "f"(b), "f"(0.f)
+        : "memory");
+}
+
 // Order-preserving map float -> int32 (and back) so integer warp reductions can take a max.
 __device__ __forceinline__ int float_order_key(float f) {
     const int i = __float_as_int(f);

@@ -262,6 +262,73 @@ struct SpecSmem {
     int abort_flag;
 };
 
+// The scan warps' route for a timestep with more uncertified states than the usual one handles;
+// out of line on purpose.  v: the thread's terms, res: its guesses (in) and, where states were
+// settled, their exact values (out); bit k of okmask: state k was certified.  Returns the number of
+// states the warp put on the list, or -1 if it settled its uncertified states here (res changed).
+template <class Topo, int NS, int SPT, int RING>
+__device__ __noinline__ int crowded_step(SpecSmem<NS, SPT, RING> &sm, const float (*v)[5], float *res, uint32_t okmask,
+                                         int par, int j, int k0, const float *in, const unsigned char *row,
+                                         float stay, const ofx::TabRef tr) {
+    constexpr int PER = SpecSmem<NS, SPT, RING>::kPerWarp;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t lt_mask = (1u << lane) - 1u;
+    uint32_t bad[SPT];
+    int total = 0;
+#pragma unroll
+    for (int k = 0; k < SPT; ++k) {
+        bad[k] = __ballot_sync(0xffffffffu, !((okmask >> k) & 1u));
+        total += __popc(bad[k]);
+    }
+    if (total > 16 * SPT) {
+        // most states uncertified (the first few dozen timesteps, where scores are small and
+        // the float grid fine): the exact routine for every state
+        float out[SPT];
+        ofx::lse5_batch_exact<SPT>(v, out, tr);
+#pragma unroll
+        for (int k = 0; k < SPT; ++k) res[k] = out[k];
+        return -1;
+    }
+    if (total > PER) {
+        // many uncertified states (the next hundred or two timesteps): settle them here and
+        // now, nothing to check later.  They are dealt out evenly to the warp's lanes, so the
+        // exact routine runs ceil(total / 32) times rather than once per state of the
+        // unluckiest lane.
+        int pos[SPT], base = 0;
+#pragma unroll
+        for (int k = 0; k < SPT; ++k) {
+            pos[k] = base + __popc(bad[k] & lt_mask);
+            if (!((okmask >> k) & 1u)) sm.redo_state[warp][pos[k]] = (unsigned short)Topo::state(j, k0 + k);
+            base += __popc(bad[k]);
+        }
+        __syncwarp();
+        for (int first = 0; first < total; first += 32) {
+            const int e = first + lane;
+            const int st = sm.redo_state[warp][e < total ? e : 0];
+            float w[5];
+            terms_of<Topo>(st, in, row, stay, w);
+            const float x = ofx::lse5_exact(w, tr, e < total);
+            if (e < total) sm.redo_value[warp][e] = x;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int k = 0; k < SPT; ++k)
+            if (!((okmask >> k) & 1u)) res[k] = sm.redo_value[warp][pos[k]];
+        return -1;
+    }
+    int base = 0;
+#pragma unroll
+    for (int k = 0; k < SPT; ++k) {
+        if (!((okmask >> k) & 1u)) {
+            float4 *entry = sm.listed[par][warp][base + __popc(bad[k] & lt_mask)];
+            entry[0] = make_float4(v[k][0], v[k][1], v[k][2], v[k][3]);
+            entry[1] = make_float4(v[k][4], res[k], __int_as_float(Topo::state(j, k0 + k)), 0.f);
+        }
+        base += __popc(bad[k]);
+    }
+    return total;
+}
+
 //
 // POST (forward direction only): the rows are not written out; a fourth kind of warp turns each
 // row, once it is final, into the posterior row  softmax_s(fwd[t][s] + bwd[t][s])  and writes
@@ -501,79 +568,49 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
         bool ok[SPT];
         thread_terms<Topo, SPT>(in, row, j, k0, stay, v, res);
         ofd::lse5_fast_guess<SPT>(v, res, ok);
-        uint32_t bad[SPT];
+        // out they go at once (certified values and guesses alike), so that the stores issue in the
+        // shadow of the vote below; the two routes that settle states here and now store again
+        thread_store<Topo, SPT>(nxt, gmem_out, j, k0, res, !POST);
         int total = 0, mine = 0;
 #pragma unroll
         for (int k = 0; k < SPT; ++k) mine += !ok[k];
+        // Both votes are taken here, where the warp is converged for certain, and nothing below
+        // votes or diverges on the usual route: a vote or a lane-divergent branch inside
+        // conditional code costs a hundred cycles and more of re-convergence.
         const uint32_t owners = __ballot_sync(0xffffffffu, mine != 0);  // non-zero about every other timestep per warp
-        // The usual case: a few lanes with one uncertified state each.  One vote settles who lists
-        // where; anything else takes the general route below.
-        const bool few = owners != 0 && __popc(owners) <= PER && !__any_sync(0xffffffffu, mine > 1);
+        const uint32_t crowded = __ballot_sync(0xffffffffu, mine > 1);
+        // The usual case: a few lanes with one uncertified state each.  The first vote settles who
+        // lists where, and the entry goes out through predicated stores.
+        const bool few = owners != 0 && crowded == 0 && __popc(owners) <= PER;
         if (few) {
-            if (mine) {
-                float4 *entry = sm.listed[i & 1][warp][__popc(owners & lt_mask)];
-#pragma unroll
-                for (int k = 0; k < SPT; ++k) {
-                    if (ok[k]) continue;
-                    entry[0] = make_float4(v[k][0], v[k][1], v[k][2], v[k][3]);
-                    entry[1] = make_float4(v[k][4], res[k], __int_as_float(Topo::state(j, k0 + k)), 0.f);
-                }
-            }
-            total = __popc(owners);
-        } else if (owners) {
-#pragma unroll
-            for (int k = 0; k < SPT; ++k) {
-                bad[k] = __ballot_sync(0xffffffffu, !ok[k]);
-                total += __popc(bad[k]);
-            }
-        }
-        if (few) {
-            // listed above
-        } else if (total > 16 * SPT) {
-            // most states uncertified (the first few dozen timesteps, where scores are small and
-            // the float grid fine): the exact routine for every state, straight from registers
-            ofx::lse5_batch_exact<SPT>(v, res, tr);
-            total = 0;
-        } else if (total > PER) {
-            // many uncertified states (the next hundred or two timesteps): settle them here and
-            // now, nothing to check later.  They are dealt out evenly to the warp's lanes, so the
-            // exact routine runs ceil(total / 32) times rather than once per state of the
-            // unluckiest lane.
-            int pos[SPT], base = 0;
-#pragma unroll
-            for (int k = 0; k < SPT; ++k) {
-                pos[k] = base + __popc(bad[k] & lt_mask);
-                if (!ok[k]) sm.redo_state[warp][pos[k]] = (unsigned short)Topo::state(j, k0 + k);
-                base += __popc(bad[k]);
-            }
-            __syncwarp();
-            for (int first = 0; first < total; first += 32) {
-                const int e = first + lane;
-                const int st = sm.redo_state[warp][e < total ? e : 0];
-                float w[5];
-                terms_of<Topo>(st, in, row, stay, w);
-                const float x = ofx::lse5_exact(w, tr, e < total);
-                if (e < total) sm.redo_value[warp][e] = x;
-            }
-            __syncwarp();
+            const uint32_t entry = (uint32_t)__cvta_generic_to_shared(sm.listed[i & 1][warp][__popc(owners & lt_mask)]);
 #pragma unroll
             for (int k = 0; k < SPT; ++k)
-                if (!ok[k]) res[k] = sm.redo_value[warp][pos[k]];
-            total = 0;
-        } else if (total) {
-            int base = 0;
+                ofd::sts_entry_if(!ok[k], entry, v[k], res[k], __int_as_float(Topo::state(j, k0 + k)));
+            total = __popc(owners);
+        } else if (owners) {
+            // anything else (a lane with two uncertified states, more than a list takes, the first
+            // few hundred timesteps where most states are uncertified) goes out of line: the
+            // loop's instructions stay few and close together.  The copies live in local memory,
+            // the arrays of the usual route in registers.
+            float cv[SPT][5], cres[SPT];
+            uint32_t okmask = 0;
 #pragma unroll
             for (int k = 0; k < SPT; ++k) {
-                if (!ok[k]) {
-                    float4 *entry = sm.listed[i & 1][warp][base + __popc(bad[k] & lt_mask)];
-                    entry[0] = make_float4(v[k][0], v[k][1], v[k][2], v[k][3]);
-                    entry[1] = make_float4(v[k][4], res[k], __int_as_float(Topo::state(j, k0 + k)), 0.f);
-                }
-                base += __popc(bad[k]);
+#pragma unroll
+                for (int q = 0; q < 5; ++q) cv[k][q] = v[k][q];
+                cres[k] = res[k];
+                okmask |= (uint32_t)ok[k] << k;
+            }
+            total = crowded_step<Topo, NS, SPT, RING>(sm, cv, cres, okmask, i & 1, j, k0, in, row, stay, tr);
+#pragma unroll
+            for (int k = 0; k < SPT; ++k) res[k] = cres[k];
+            if (total < 0) {  // states were settled here and now: their values replace the guesses
+                thread_store<Topo, SPT>(nxt, gmem_out, j, k0, res, !POST);
+                total = 0;
             }
         }
         if (lane == 0) sm.n_listed[i & 1][warp] = total;
-        thread_store<Topo, SPT>(nxt, gmem_out, j, k0, res, !POST);
         if (__syncthreads_or(0)) {
             __syncthreads();  // the checker is correcting this row's readers
 #pragma unroll
