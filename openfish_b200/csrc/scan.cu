@@ -157,7 +157,9 @@ __device__ __forceinline__ void thread_store(float *smem_row, float *gmem_row, i
 
 // ------------------------------------------------------------------------------------------
 // One row of the posterior, softmax_s(fwd[s] + bwd[s]), by one warp: the forward row comes from
-// shared memory, the backward row was fetched from HBM into registers a timestep earlier.  Lane l
+// shared memory and so does the backward row (it arrives beside the score row of the timestep
+// during which it is needed; a load from HBM issued by this warp would put a microsecond of
+// latency into every timestep, which is more than the scan warps take).  Lane l
 // takes the states (q*32 + l)*VEC .. +VEC-1; the arithmetic and its order are those of the
 // stand-alone posterior loop in posterior_seq.cu (softmax offset m0 = the maximum of row 0, where
 // fwd is zero: the log partition function is the same for every row, so exponents stay in range).
@@ -166,7 +168,6 @@ struct PosteriorRow {
     static constexpr int PERL = NS / 32;
     static constexpr int VEC = PERL >= 4 ? 4 : PERL;
     static constexpr int NV = PERL / VEC;
-    float b[PERL];
 
     __device__ static float row_max(const float *row, int lane) {
         float m = -3.0e38f;
@@ -184,22 +185,19 @@ struct PosteriorRow {
             d[0] = *p;
         }
     }
-    __device__ void fetch(const float *bwd_row, int lane) {
-#pragma unroll
-        for (int q = 0; q < NV; ++q) load(b + q * VEC, bwd_row + (q * 32 + lane) * VEC);
-    }
-    // (the exponentials take the place of the backward row: fetch the next one afterwards)
-    __device__ void emit(const float *fwd_row, float *post_row, float m0, int lane) {
+    __device__ static void emit(const float *fwd_row, const float *bwd_row, float *post_row, float m0, int lane) {
         const float kLog2e = 1.4426950408889634f;
+        float e[PERL];
         float part = 0.f;
 #pragma unroll
         for (int q = 0; q < NV; ++q) {
-            float f[VEC];
+            float f[VEC], b[VEC];
             load(f, fwd_row + (q * 32 + lane) * VEC);
+            load(b, bwd_row + (q * 32 + lane) * VEC);
 #pragma unroll
             for (int k = 0; k < VEC; ++k) {
-                b[q * VEC + k] = ofd::ex2_approx(((f[k] + b[q * VEC + k]) - m0) * kLog2e);
-                part += b[q * VEC + k];
+                e[q * VEC + k] = ofd::ex2_approx(((f[k] + b[k]) - m0) * kLog2e);
+                part += e[q * VEC + k];
             }
         }
 #pragma unroll
@@ -208,13 +206,13 @@ struct PosteriorRow {
 #pragma unroll
         for (int q = 0; q < NV; ++q) {
             float *p = post_row + (q * 32 + lane) * VEC;
-            const float *e = b + q * VEC;
+            const float *x = e + q * VEC;
             if constexpr (VEC == 4)
-                *reinterpret_cast<float4 *>(p) = make_float4(e[0] * inv, e[1] * inv, e[2] * inv, e[3] * inv);
+                *reinterpret_cast<float4 *>(p) = make_float4(x[0] * inv, x[1] * inv, x[2] * inv, x[3] * inv);
             else if constexpr (VEC == 2)
-                *reinterpret_cast<float2 *>(p) = make_float2(e[0] * inv, e[1] * inv);
+                *reinterpret_cast<float2 *>(p) = make_float2(x[0] * inv, x[1] * inv);
             else
-                *p = e[0] * inv;
+                *p = x[0] * inv;
         }
     }
 };
@@ -238,12 +236,15 @@ struct PosteriorRow {
 // value, what the exact routine alone would have produced.  Three row buffers rotate so that the
 // inputs of a timestep are still there while it is being checked, and score rows are released
 // one timestep late.
-template <int NS, int SPT, int RING>
+template <int NS, int SPT, int RING, bool POST>
 struct SpecSmem {
     static constexpr int kRowBytes = NS * 4 * 2;
     static constexpr int NW = NS / SPT / 32;  // scan warps
     static constexpr int kPerWarp = 16;       // listed states per warp and timestep, at most
     alignas(128) unsigned char ring[RING][kRowBytes];
+    // with the posterior: the backward row that the posterior warp needs during a timestep
+    // travels with that timestep's score row (same slot, same mbarrier)
+    alignas(128) float bwd_ring[POST ? RING : 1][POST ? NS : 4];
     alignas(16) float alpha[3][NS];
     alignas(16) double exp2_rep[ofx::kExpTab * kExpCopies];
     double rcp_c[ofx::kLogTab];
@@ -266,11 +267,11 @@ struct SpecSmem {
 // out of line on purpose.  v: the thread's terms, res: its guesses (in) and, where states were
 // settled, their exact values (out); bit k of okmask: state k was certified.  Returns the number of
 // states the warp put on the list, or -1 if it settled its uncertified states here (res changed).
-template <class Topo, int NS, int SPT, int RING>
-__device__ __noinline__ int crowded_step(SpecSmem<NS, SPT, RING> &sm, const float (*v)[5], float *res, uint32_t okmask,
+template <class Topo, int NS, int SPT, int RING, bool POST>
+__device__ __noinline__ int crowded_step(SpecSmem<NS, SPT, RING, POST> &sm, const float (*v)[5], float *res, uint32_t okmask,
                                          int par, int j, int k0, const float *in, const unsigned char *row,
                                          float stay, const ofx::TabRef tr) {
-    constexpr int PER = SpecSmem<NS, SPT, RING>::kPerWarp;
+    constexpr int PER = SpecSmem<NS, SPT, RING, POST>::kPerWarp;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t lt_mask = (1u << lane) - 1u;
     uint32_t bad[SPT];
@@ -343,7 +344,7 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
                                           const ofx::Tables *tables, int *status, uint64_t wait_ns) {
     constexpr int NJ = NS / 4;
     constexpr int TPC = NS / SPT;
-    using Smem = SpecSmem<NS, SPT, RING>;
+    using Smem = SpecSmem<NS, SPT, RING, POST>;
     constexpr int NW = Smem::NW, PER = Smem::kPerWarp;
     static_assert(!POST || Topo::kForward, "the posterior rides on the forward scan");
     static_assert(TPC % 32 == 0, "scan warps must be full");
@@ -379,9 +380,13 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
         auto fill = [&](int i) {
             if (sm.abort_flag) return;
             const int slot = i % RING;
-            ofd::mbar_arrive_expect_tx(&sm.full[slot], Smem::kRowBytes);
+            ofd::mbar_arrive_expect_tx(&sm.full[slot], Smem::kRowBytes + (POST ? NS * 4 : 0));
             ofd::bulk_g2s(sm.ring[slot], chunk_scores + t_stride * (size_t)Topo::score_row(i, T), Smem::kRowBytes,
                           &sm.full[slot]);
+            // the posterior row formed during timestep i is row i-1 (row 0 during timestep 0)
+            if (POST)
+                ofd::bulk_g2s(sm.bwd_ring[slot], bwd_in + ((size_t)chunk * (size_t)(T + 1) + (size_t)(i ? i - 1 : 0)) * NS,
+                              NS * 4, &sm.full[slot]);
             ++issued;
         };
         auto landed = [&](int i) {
@@ -407,28 +412,27 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
         // ------------------------------------------------------------------ posterior warp
         const float *bwd_chunk = bwd_in + (size_t)chunk * (size_t)(T + 1) * NS;
         const float m0 = PosteriorRow<NS>::row_max(bwd_chunk, lane);
-        PosteriorRow<NS> pr;
-        auto fetch = [&](int r) { pr.fetch(bwd_chunk + (size_t)r * NS, lane); };
-        auto emit = [&](int r) { pr.emit(sm.alpha[r % 3], out_chunk + (size_t)r * NS, m0, lane); };
-        fetch(0);
+        // inside the scan the backward row is in the slot of the timestep during which the
+        // posterior row is formed; the last two rows take theirs from HBM
+        auto emit = [&](int r, const float *bwd_row) {
+            PosteriorRow<NS>::emit(sm.alpha[r % 3], bwd_row, out_chunk + (size_t)r * NS, m0, lane);
+        };
         __syncthreads();  // start of the scan
         int next_row = 0;
         for (int i = 0; i < T; ++i) {
             // during timestep i the rows up to i-1 are final (and row 0 always is)
             if (next_row == 0 || next_row <= i - 1) {
-                emit(next_row);
+                emit(next_row, sm.bwd_ring[i % RING]);  // next_row = i-1, or 0 when i = 0
                 ++next_row;
-                fetch(next_row);  // next_row <= T
             }
             if (__syncthreads_or(0)) __syncthreads();
         }
         while (next_row <= T - 1) {  // final since the last timestep's barrier
-            emit(next_row);
+            emit(next_row, bwd_chunk + (size_t)next_row * NS);
             ++next_row;
-            fetch(next_row);
         }
         __syncthreads();  // the last row is final
-        emit(T);
+        emit(T, bwd_chunk + (size_t)T * NS);
         return;
     }
 
@@ -602,7 +606,7 @@ __device__ __forceinline__ void spec_body(unsigned char *smem_raw, int chunk, co
                 cres[k] = res[k];
                 okmask |= (uint32_t)ok[k] << k;
             }
-            total = crowded_step<Topo, NS, SPT, RING>(sm, cv, cres, okmask, i & 1, j, k0, in, row, stay, tr);
+            total = crowded_step<Topo, NS, SPT, RING, POST>(sm, cv, cres, okmask, i & 1, j, k0, in, row, stay, tr);
 #pragma unroll
             for (int k = 0; k < SPT; ++k) res[k] = cres[k];
             if (total < 0) {  // states were settled here and now: their values replace the guesses
@@ -657,7 +661,7 @@ scan_spec_posterior_kernel(const __half *__restrict__ scores, const float *__res
 template <int NS, int SPT, int RING>
 cudaError_t launch_spec(const __half *scores, float *bwd, float *fwd, int T, int N, float stay,
                         const ofx::Tables *tables, int *status, uint64_t wait_ns, cudaStream_t stream) {
-    using Smem = SpecSmem<NS, SPT, RING>;
+    using Smem = SpecSmem<NS, SPT, RING, false>;
     const size_t bytes = sizeof(Smem) + 128;
     auto kern = scan_spec_kernel<NS, SPT, RING>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
@@ -670,7 +674,7 @@ cudaError_t launch_spec(const __half *scores, float *bwd, float *fwd, int T, int
 template <int NS, int SPT, int RING>
 cudaError_t launch_spec_posterior(const __half *scores, const float *bwd, float *post, int T, int N, float stay,
                                   const ofx::Tables *tables, int *status, uint64_t wait_ns, cudaStream_t stream) {
-    using Smem = SpecSmem<NS, SPT, RING>;
+    using Smem = SpecSmem<NS, SPT, RING, true>;
     const size_t bytes = sizeof(Smem) + 128;
     auto kern = scan_spec_posterior_kernel<NS, SPT, RING>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
