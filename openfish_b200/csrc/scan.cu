@@ -225,8 +225,8 @@ struct PosteriorRow {
 // nearly every step: almost every timestep has a few such states.  Here the scan warps do not
 // wait for it.  An uncertified state gets the likelier of its two candidate floats and is put on
 // a list, together with its five terms; while the scan warps work on the next timestep, a
-// checker warp recomputes the listed states exactly.  If every guess was right (about three timesteps in
-// four) nothing else happens.  If one was wrong the block pauses at the end of that next
+// checker warp recomputes the listed states exactly.  If every guess was right (most timesteps)
+// nothing else happens.  If one was wrong the block pauses at the end of that next
 // timestep: the checker corrects the value and recomputes exactly the five states of the next
 // row that read it (the state itself and its four readers) before anybody reads those, and the
 // scan carries on.  (Letting the scan run on and chasing the consequences a step behind does
