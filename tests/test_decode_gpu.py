@@ -399,6 +399,13 @@ def test_scores_with_the_blank_column_inside(native_lib, oracle_mod, sl, T, N, c
         of.decode_5wide_into(late, sl, gb, *out, clamp=clamp, stream=side)
     for k, o in zip(("moves", "sequence", "qstring"), out):
         assert np.array_equal(o.numpy(), got[k]), k
+    # the strip's device time is reported beside the decode's, and only for a 5-wide call
+    assert gb.last_decode_ms()["strip_blank"] > 0.0
+    four = torch.from_numpy(np.ascontiguousarray(want4.astype(np.float16))).cuda()
+    of.decode_into(four, sl, gb, *out)
+    assert gb.last_decode_ms()["strip_blank"] == 0.0
+    for k, o in zip(("moves", "sequence", "qstring"), out):
+        assert np.array_equal(o.numpy(), got[k]), k
     gb.free()
 
 
