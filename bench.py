@@ -502,9 +502,7 @@ def main():
     api_wall = []
     for _ in range(10):
         torch.cuda.synchronize()
-        a0 = time.perf_counter()
-        of.decode_gpu(scores, STATE_LEN, gpubuf=gb)
-        api_wall.append(1e3 * (time.perf_counter() - a0))
+        api_wall.append(of.decode_gpu_wall_ms(scores, STATE_LEN, gb))
     rotary = measure_rotary(of, dev, cpu_too=(world == 1 and not args.no_cpu_baseline)) if rank == 0 else None
 
     # ---- outside the timed regions ---------------------------------------------------------

@@ -197,6 +197,24 @@ def decode_gpu(scores_TNC, state_len, options=None, gpubuf=None):
             gpubuf.free()
 
 
+def decode_gpu_wall_ms(scores_TNC, state_len, gpubuf, options=None):
+    """Wall-clock milliseconds of one openfish_decode_gpu call by itself (what the reference's driver
+    times, src/main.c:271-303): the clock runs around the C call only; the malloc'ed results are
+    freed afterwards without being copied into Python objects."""
+    import time
+    args = _scores_args(scores_TNC, state_len, options, gpubuf)
+    out = [C.c_void_p() for _ in range(3)]
+    refs = [C.byref(o) for o in out]
+    fn = lib().openfish_decode_gpu
+    t0 = time.perf_counter()
+    fn(*args, *refs)
+    ms = 1e3 * (time.perf_counter() - t0)
+    _check()
+    for p in out:
+        lib().libc_free(p)
+    return ms
+
+
 def decode_into(scores_TNC, state_len, gpubuf, moves, sequence, qstring, options=None, wait=True, stream=None):
     """openfish_b200_decode_into / _submit / _submit_on: results into caller-owned uint8 host
     tensors [N][T] (torch, ideally pinned).  With wait=False call decode_wait(gpubuf) afterwards.

@@ -223,7 +223,16 @@ void openfish_decode_gpu(const int T, const int N, const int C, void *scores_TNC
         raise_error(__func__, OPENFISH_B200_ERR_ALLOC, "could not allocate the result buffers");
         return;
     }
-    openfish_b200_decode_into(T, N, C, scores_TNC, state_len, options, gpubuf, m, s, q);
+    openfish_b200_decode_submit(T, N, C, scores_TNC, state_len, options, gpubuf, m, s, q);
+    if (t_status == OPENFISH_B200_OK) {
+        /* Fresh allocations of this size are untouched pages: writing to them for the first time
+         * costs a page fault per 4 KB (a quarter of a millisecond for a 512-chunk batch).  That
+         * is paid here, while the GPU is busy, instead of in the copy after the wait. */
+        memset(m, 0, nt);
+        memset(s, 0, nt);
+        memset(q, 0, nt);
+        openfish_b200_decode_wait(gpubuf);
+    }
     if (t_status != OPENFISH_B200_OK) {
         free(m); free(s); free(q);
         return;
